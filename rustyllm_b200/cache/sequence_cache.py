@@ -11,8 +11,8 @@ sequence.  Here one pool serves every sequence of every batch:
   * a *slot* holds one sequence: its length, one row of each group's page table,
     and ``state_bytes`` of state that is zeroed when the slot is handed out;
   * a *group* is the storage of all layers with the same need (number of KV
-    heads, width of a key head and of a value head, all keys or a window of them, with
-    or without first positions that stay).
+    heads, width of a key head and of a value head, all keys, a window of them or the
+    current block of a chunked mask, with or without first positions that stay).
     It owns the keys ``[layers, pages, kv_heads, page_size, head_dim]``, the values
     ``[layers, pages, kv_heads, page_size, value_dim]`` and a page allocator;
     page p of a slot holds positions ``[p*page_size, (p+1)*page_size)`` of every
@@ -41,10 +41,14 @@ class KVNeed:
     num_kv_heads: int
     head_dim: int                  # width of a key head
     window: Optional[int] = None   # None: all keys; W: only the last W positions are read
-    value_dim: Optional[int] = None  # width of a value head; None: the same as head_dim
+    value_dim: Optional[int] = None  # width of a value head; None: the same as head_dim; 0: no values are stored
+                                     # (a mixer whose values are a part of its key rows)
     keep_first: int = 0            # with a window: positions [0, keep_first) stay readable for good
+    chunk: Optional[int] = None    # C: a query at position i reads positions [i - i % C, i] only (excludes a window)
 
     def __post_init__(self):
+        if self.chunk is not None and self.window is not None:
+            raise ValueError("a chunked mask and a window exclude one another")
         if self.window is None and self.keep_first:
             object.__setattr__(self, "keep_first", 0)   # without a window everything stays anyway
         if self.value_dim == self.head_dim:        # one way to say "the same": equal needs share a group
@@ -240,12 +244,13 @@ class SequenceCache:
         for s, n in zip(slots, counts):
             self.lengths[s] += n
         for g in self.groups:
-            w = g.need.window
-            if w is None:
+            w, c = g.need.window, g.need.chunk
+            if w is None and c is None:
                 continue
             for s in slots:
-                # the next query sits at position len; it reads positions >= len + 1 - w
-                first_needed = max(0, self.lengths[s] + 1 - w)
+                # the next query sits at position len; it reads positions >= len + 1 - w (a window),
+                # or those of its own block of c positions (a chunked mask)
+                first_needed = max(0, self.lengths[s] + 1 - w) if c is None else self.lengths[s] - self.lengths[s] % c
                 dead = first_needed // PAGE_SIZE   # logical pages wholly in front of it
                 kept = -(-g.need.keep_first // PAGE_SIZE)   # pages that hold a position the window never drops
                 sp = g.slot_pages[s]

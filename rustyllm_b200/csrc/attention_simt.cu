@@ -2,7 +2,9 @@
 // cores, for any head size up to 256 (steps of 2), any number of heads and groups,
 // float or bf16 storage.  Serves prefill and decode alike: a query token at
 // position p attends to cached positions [max(0, p + 1 - window), p] of its own
-// sequence, which the rope/cache-write kernel has filled before this runs.
+// sequence (with `chunk` > 0 instead: to [p - p % chunk, p], the positions of its own
+// block of `chunk` positions counted from the sequence's start), which the rope/cache-write
+// kernel has filled before this runs.
 //
 // Formulas (SimonWaldherr/RustyLLM): query head h uses KV head g = h / (H/G)
 // (src/model.rs:6034-6198); score_t = (q_h . K[t, g]) / sqrt(head_dim); streaming
@@ -30,7 +32,8 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
                       const T* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
                       const int* __restrict__ slot_of_token, const int* __restrict__ positions,
                       T* __restrict__ out, int ldo, int H, int G, int hd, int vd, float scale, int window,
-                      int sink, const T* __restrict__ gate, int ldg, float softcap, int keep_first) {
+                      int sink, const T* __restrict__ gate, int ldg, float softcap, int keep_first, int chunk, int ldv,
+                      int gate_per_head) {
   constexpr int NE = ATT_MAX_HD / 32;
   __shared__ float s_acc[ATT_WARPS][ATT_MAX_HD];
   __shared__ float s_max[ATT_WARPS], s_sum[ATT_WARPS];
@@ -48,7 +51,7 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
     qv[e] = d < hd ? rl_ld(qrow + d) * scale : 0.f;
   }
 
-  const int start = (window > 0 && pos + 1 - window > 0) ? pos + 1 - window : 0;
+  const int start = chunk > 0 ? pos - pos % chunk : (window > 0 && pos + 1 - window > 0) ? pos + 1 - window : 0;
   // kept first tokens: positions [0, nfirst) in front of the window are seen as well.  The keys are walked
   // as one run of `total` places: place v is position v for v < nfirst and start + (v - nfirst) behind.
   const int nfirst = min(keep_first, start);
@@ -58,8 +61,10 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
 #pragma unroll
   for (int e = 0; e < NE; ++e) acc[e] = 0.f;
   float run_max = -INFINITY, run_sum = 0.f;
-  const size_t head_off = (size_t)g * RL_PAGE * hd, v_head_off = (size_t)g * RL_PAGE * vd;
-  const size_t page_stride = (size_t)G * RL_PAGE * hd, v_page_stride = (size_t)G * RL_PAGE * vd;
+  // a value row is `ldv` elements long (its first vd are the value): ldv = vd for a pool of values of its own,
+  // ldv = hd where the values are the front part of the key rows and v_pool is the key pool
+  const size_t head_off = (size_t)g * RL_PAGE * hd, v_head_off = (size_t)g * RL_PAGE * ldv;
+  const size_t page_stride = (size_t)G * RL_PAGE * hd, v_page_stride = (size_t)G * RL_PAGE * ldv;
 
   for (int v0 = 32 * warp; v0 < total; v0 += 32 * ATT_WARPS) {
     const int n = min(32, total - v0);
@@ -88,7 +93,7 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
     for (int j = 0; j < n; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const int tj = v0 + j < nfirst ? v0 + j : start + (v0 + j - nfirst);
-      const T* vrow = v_pool + (size_t)pages[tj / RL_PAGE] * v_page_stride + v_head_off + (size_t)(tj % RL_PAGE) * vd;
+      const T* vrow = v_pool + (size_t)pages[tj / RL_PAGE] * v_page_stride + v_head_off + (size_t)(tj % RL_PAGE) * ldv;
 #pragma unroll
       for (int e = 0; e < NE; ++e) {
         const int d = lane + 32 * e;
@@ -121,7 +126,8 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
 #pragma unroll
     for (int w = 0; w < ATT_WARPS; ++w) o += s_acc[w][d] * wgt[w];
     o *= inv;
-    if (gate) o *= 1.0f / (1.0f + expf(-rl_ld(gate + (size_t)m * ldg + (size_t)h * vd + d)));   // output gate, in 32-bit
+    if (gate)       // output gate, in 32-bit: a number for every output element, or one for the head
+      o *= 1.0f / (1.0f + expf(-rl_ld(gate + (size_t)m * ldg + (gate_per_head ? (size_t)h : (size_t)h * vd + d))));
     rl_st(orow + d, o);
   }
 }
@@ -137,14 +143,22 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
 //
 // softcap > 0: every score s (scale included) becomes softcap * tanh(s / softcap).  keep_first > 0 (with a window):
 // a query also sees positions [0, keep_first) that the window has left behind.
-extern "C" int rl_attention_simt_masked(const void* q, int ldq, const void* k_pool, const void* v_pool,
+//
+// chunk > 0 (instead of a window): a query at position p sees positions [p - p % chunk, p].  value_stride: elements
+// from one value row to the next (0: value_dim); with value_stride = head_dim and v_pool = k_pool the values are the
+// first value_dim elements of the key rows.  gate_per_head != 0: gate is [M, ldg] with one number a head.
+extern "C" int rl_attention_simt_shaped(const void* q, int ldq, const void* k_pool, const void* v_pool,
                                         int dtype, const int* page_table, int max_pages,
                                         const int* slot_of_token, const int* positions, void* out, int ldo,
                                         int num_tokens, int num_heads, int num_kv_heads, int head_dim, int value_dim,
                                         float scale, int window, int sink, const void* gate, int ldg, float softcap,
-                                        int keep_first, cudaStream_t stream) {
+                                        int keep_first, int chunk, int value_stride, int gate_per_head, cudaStream_t stream) {
+  RL_REQUIRE(chunk >= 0 && !(chunk > 0 && window > 0), "rl_attention_simt: a chunked mask and a window exclude one another");
+  RL_REQUIRE(value_stride == 0 || value_stride >= value_dim, "rl_attention_simt: value rows %d apart are shorter than a value (%d)",
+             value_stride, value_dim);
+  const int ldv = value_stride ? value_stride : value_dim;
   RL_REQUIRE(softcap >= 0.f && keep_first >= 0, "rl_attention_simt: negative soft cap or number of kept first tokens");
-  RL_REQUIRE(gate == nullptr || ldg >= num_heads * value_dim, "rl_attention_simt: the gate's row stride is too small");
+  RL_REQUIRE(gate == nullptr || ldg >= (gate_per_head ? num_heads : num_heads * value_dim), "rl_attention_simt: the gate's row stride is too small");
   RL_REQUIRE(num_tokens >= 0 && num_heads > 0 && num_kv_heads > 0, "rl_attention_simt: bad sizes");
   RL_REQUIRE(num_heads % num_kv_heads == 0, "rl_attention_simt: %d heads are no multiple of %d KV heads",
              num_heads, num_kv_heads);
@@ -159,16 +173,27 @@ extern "C" int rl_attention_simt_masked(const void* q, int ldq, const void* k_po
     attention_simt_kernel<float><<<grid, ATT_WARPS * 32, 0, stream>>>(
         (const float*)q, ldq, (const float*)k_pool, (const float*)v_pool, page_table, max_pages,
         slot_of_token, positions, (float*)out, ldo, num_heads, num_kv_heads, head_dim, value_dim, scale, window,
-        sink, (const float*)gate, ldg, softcap, keep_first);
+        sink, (const float*)gate, ldg, softcap, keep_first, chunk, ldv, gate_per_head);
   else if (dtype == RL_BF16)
     attention_simt_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, 0, stream>>>(
         (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table,
         max_pages, slot_of_token, positions, (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, head_dim, value_dim, scale, window,
-        sink, (const __nv_bfloat16*)gate, ldg, softcap, keep_first);
+        sink, (const __nv_bfloat16*)gate, ldg, softcap, keep_first, chunk, ldv, gate_per_head);
   else
     RL_REQUIRE(false, "rl_attention_simt: unknown dtype %d", dtype);
   RL_LAUNCH_CHECK("rl_attention_simt");
   return RL_OK;
+}
+
+extern "C" int rl_attention_simt_masked(const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                        int dtype, const int* page_table, int max_pages,
+                                        const int* slot_of_token, const int* positions, void* out, int ldo,
+                                        int num_tokens, int num_heads, int num_kv_heads, int head_dim, int value_dim,
+                                        float scale, int window, int sink, const void* gate, int ldg, float softcap,
+                                        int keep_first, cudaStream_t stream) {
+  return rl_attention_simt_shaped(q, ldq, k_pool, v_pool, dtype, page_table, max_pages, slot_of_token, positions, out, ldo,
+                                  num_tokens, num_heads, num_kv_heads, head_dim, value_dim, scale, window, sink, gate, ldg, softcap,
+                                  keep_first, 0, 0, 0, stream);
 }
 
 extern "C" int rl_attention_simt_gated(const void* q, int ldq, const void* k_pool, const void* v_pool,

@@ -306,6 +306,113 @@ extern "C" int rl_embedding_pos(const void* table, const void* pos_table, int ta
   return RL_OK;
 }
 
+// ------------------------------------------------------------------ scaled embedding with a hashed pair table
+// x[m, :] = E[token_m, :] * scale + P[row_m, :], in 32-bit.  row_m = (prev_m * mul_prev + token_m * mul_cur) mod buckets,
+// where prev_m is the token in front of token m in its sequence; a sequence's first token takes row `buckets` (the
+// table has buckets + 1 rows).  The token in front of a step's first token of a sequence is per-slot state (an
+// int32 a slot): the block of that first token reads it and then leaves the sequence's last token of this step
+// there - it is the only block that touches the slot's entry, so nothing races.  pair_table null: the scaled
+// embedding alone (the state is still kept).
+template <typename T>
+__global__ void embedding_pair_kernel(const T* __restrict__ table, const T* __restrict__ pair_table, const int* __restrict__ ids,
+                                      const int* __restrict__ positions, const int* __restrict__ slot_of_token,
+                                      const int* __restrict__ cu_seqlens, int num_seqs, int* __restrict__ last_token,
+                                      long long state_stride, float scale, long long mul_prev, long long mul_cur, int buckets,
+                                      float* __restrict__ out, int d, int vocab, int* __restrict__ err) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  __shared__ int s_prev;
+  const int m = blockIdx.x;
+  int id = ids[m];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicExch(err, 1);
+    id = 0;
+  }
+  if (threadIdx.x == 0) {
+    const int slot = slot_of_token[m];
+    const bool first_of_step = m == 0 || slot_of_token[m - 1] != slot;
+    int prev = -1;
+    if (!first_of_step) {
+      prev = ids[m - 1];
+    } else {
+      int* st = last_token + (size_t)slot * state_stride;
+      if (positions[m] > 0) prev = *st;
+      int lo = 0, hi = num_seqs;            // the sequence b with cu_seqlens[b] <= m < cu_seqlens[b + 1]
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (cu_seqlens[mid] <= m) lo = mid; else hi = mid;
+      }
+      *st = ids[cu_seqlens[lo + 1] - 1];
+    }
+    if (prev >= vocab) prev = 0;            // a bad id was reported where it was read as a token
+    s_prev = prev;
+  }
+  __syncthreads();
+  const int prev = s_prev;
+  const T* row = table + (size_t)id * d;
+  float* o = out + (size_t)m * d;
+  if (pair_table) {
+    const long long r = prev < 0 ? (long long)buckets : ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+    const T* prow = pair_table + (size_t)r * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = fmaf(rl_ld(row + i), scale, rl_ld(prow + i));
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = rl_ld(row + i) * scale;
+  }
+}
+
+// last_token: int32, one entry a slot, `state_stride` ints apart.  mul_prev, mul_cur >= 0, buckets > 0 with a pair table.
+extern "C" int rl_embedding_pair(const void* table, const void* pair_table, int table_dtype, const int* ids, const int* positions,
+                                 const int* slot_of_token, const int* cu_seqlens, int num_seqs, int* last_token,
+                                 long long state_stride, float scale, long long mul_prev, long long mul_cur, int buckets,
+                                 float* out, int num_tokens, int hidden, int vocab, int* err, cudaStream_t stream) {
+  RL_REQUIRE(num_tokens >= 0 && hidden > 0 && vocab > 0 && num_seqs >= 0, "rl_embedding_pair: bad sizes M=%d d=%d V=%d B=%d",
+             num_tokens, hidden, vocab, num_seqs);
+  RL_REQUIRE(err != nullptr && last_token != nullptr, "rl_embedding_pair: the error flag or the state pointer is null");
+  RL_REQUIRE(pair_table == nullptr || (buckets > 0 && mul_prev >= 0 && mul_cur >= 0), "rl_embedding_pair: bad hash constants");
+  if (num_tokens == 0) return RL_OK;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (table_dtype == RL_F32)
+    rl_launch_pdl(embedding_pair_kernel<float>, num_tokens, threads, 0, stream, (const float*)table, (const float*)pair_table, ids,
+                  positions, slot_of_token, cu_seqlens, num_seqs, last_token, state_stride, scale, mul_prev, mul_cur, buckets, out,
+                  hidden, vocab, err);
+  else if (table_dtype == RL_BF16)
+    rl_launch_pdl(embedding_pair_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (const __nv_bfloat16*)table,
+                  (const __nv_bfloat16*)pair_table, ids, positions, slot_of_token, cu_seqlens, num_seqs, last_token, state_stride,
+                  scale, mul_prev, mul_cur, buckets, out, hidden, vocab, err);
+  else
+    RL_REQUIRE(false, "rl_embedding_pair: unknown table dtype %d", table_dtype);
+  RL_LAUNCH_CHECK("rl_embedding_pair");
+  return RL_OK;
+}
+
+// ------------------------------------------------------------------ gelu, tanh form
+// out = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), in 32-bit, rounded once at the store.
+template <typename T>
+__global__ void gelu_tanh_kernel(const T* __restrict__ in, T* __restrict__ out, size_t total) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const float z = rl_ld(in + i);
+    rl_st(out + i, 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))));
+  }
+}
+
+extern "C" int rl_gelu_tanh(const void* in, void* out, int dtype, long long total, cudaStream_t stream) {
+  RL_REQUIRE(total >= 0, "rl_gelu_tanh: negative size");
+  if (total == 0) return RL_OK;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == RL_F32)
+    rl_launch_pdl(gelu_tanh_kernel<float>, blocks, threads, 0, stream, (const float*)in, (float*)out, (size_t)total);
+  else if (dtype == RL_BF16)
+    rl_launch_pdl(gelu_tanh_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out,
+                  (size_t)total);
+  else
+    RL_REQUIRE(false, "rl_gelu_tanh: unknown dtype %d", dtype);
+  RL_LAUNCH_CHECK("rl_gelu_tanh");
+  return RL_OK;
+}
+
 // ------------------------------------------------------------------ additions to the residual between layers
 // x[m, :] += (again ? again[m, :] : 0) + (vec ? vec[:] : 0), all float: what a model adds to the
 // residual stream where a group of layers is entered (a copy of an earlier state of the stream,

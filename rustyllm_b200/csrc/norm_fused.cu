@@ -1,8 +1,9 @@
 // Norms on a sublayer's output, fused with what stands around them.  All arithmetic is 32-bit.
 //
-// rl_norm_add     x += rms_norm(s0 * y0 + s1 * y1) * w      (a layer that norms what its sublayer returns
-//                 before it joins the stream; two terms for two mixers side by side); optionally the new x
-//                 is also left as bf16 for the next sublayer's first product
+// rl_norm_add     x += m * rms_norm(s0 * y0 + s1 * y1) * w  (a layer that norms what its sublayer returns
+//                 before it joins the stream; two terms for two mixers side by side; m: a constant of the
+//                 model on every normed sublayer output); optionally the new x is also left as bf16 for the
+//                 next sublayer's first product
 // rl_gated_norm   the output of a recurrent mixer: y * act(gate), an RMS norm in `groups` equal parts, times w
 //                 ("gate first"), or the norm of y over the row times w, then times act(gate) ("gate last")
 // rl_gelu_gate    out = gelu_tanh(t) * table[token, col0 : col0 + n]    (a learned vector per token and layer
@@ -27,7 +28,7 @@ __device__ __forceinline__ float nf_block_sum(float v, float* s_part) {
 
 __global__ void __launch_bounds__(NF_THREADS)
 norm_add_kernel(float* __restrict__ x, const float* __restrict__ y0, float s0, const float* __restrict__ y1, float s1,
-                const float* __restrict__ w, float eps, int d, __nv_bfloat16* __restrict__ x_bf16) {
+                const float* __restrict__ w, float eps, float out_scale, int d, __nv_bfloat16* __restrict__ x_bf16) {
   __shared__ float s_part[NF_THREADS / 32];
   rl_pdl_trigger();
   rl_pdl_wait();
@@ -40,7 +41,7 @@ norm_add_kernel(float* __restrict__ x, const float* __restrict__ y0, float s0, c
   const float r = 1.0f / sqrtf(nf_block_sum(ss, s_part) / (float)d + eps);
   for (int i = threadIdx.x; i < d; i += NF_THREADS) {
     const float v = y1 ? fmaf(s1, y1[row + i], s0 * y0[row + i]) : s0 * y0[row + i];
-    const float nx = x[row + i] + v * r * w[i];
+    const float nx = x[row + i] + out_scale * (v * r * w[i]);
     x[row + i] = nx;
     if (x_bf16) x_bf16[row + i] = __float2bfloat16_rn(nx);
   }
@@ -117,10 +118,10 @@ gelu_gate_kernel(const T* __restrict__ t, int ldt, const int* __restrict__ token
 }
 
 extern "C" int rl_norm_add(float* x, const float* y0, float s0, const float* y1, float s1, const float* weight, float eps,
-                           int num_tokens, int width, void* x_bf16, cudaStream_t stream) {
+                           float out_scale, int num_tokens, int width, void* x_bf16, cudaStream_t stream) {
   RL_REQUIRE(num_tokens >= 0 && width > 0 && y0 != nullptr && weight != nullptr, "rl_norm_add: bad arguments");
   if (num_tokens == 0) return RL_OK;
-  rl_launch_pdl(norm_add_kernel, num_tokens, NF_THREADS, 0, stream, x, y0, s0, y1, s1, weight, eps, width, (__nv_bfloat16*)x_bf16);
+  rl_launch_pdl(norm_add_kernel, num_tokens, NF_THREADS, 0, stream, x, y0, s0, y1, s1, weight, eps, out_scale, width, (__nv_bfloat16*)x_bf16);
   RL_LAUNCH_CHECK("rl_norm_add");
   return RL_OK;
 }

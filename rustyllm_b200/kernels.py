@@ -50,6 +50,18 @@ _SIGNATURES = {
     "rl_attention_simt_masked": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
                                  _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                                  _c_int, _c_void_p, _c_int, _c_float, _c_int, _c_void_p],
+    "rl_attention_simt_shaped": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
+                                 _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
+                                 _c_int, _c_void_p, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "rl_embedding_pair": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll,
+                          _c_float, _c_ll, _c_ll, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "rl_gelu_tanh": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
+    "rl_qk_rotate_unit": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+                          _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    "rl_latent_prepare": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_int,
+                          _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "rl_latent_query": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p,
+                        _c_int, _c_int, _c_int, _c_void_p],
     "rl_short_conv": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_ll,
                       _c_void_p, _c_int, _c_int, _c_void_p],
     "rl_short_conv_state": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll, _c_void_p],
@@ -59,7 +71,8 @@ _SIGNATURES = {
     "rl_linear_scan": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
                        _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll, _c_void_p, _c_int, _c_int,
                        _c_int, _c_int, _c_int, _c_int, _c_void_p],
-    "rl_norm_add": [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_float, _c_void_p, _c_float, _c_int, _c_int, _c_void_p, _c_void_p],
+    "rl_norm_add": [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_float, _c_void_p, _c_float, _c_float, _c_int, _c_int, _c_void_p,
+                    _c_void_p],
     "rl_gated_norm": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_int, _c_int, _c_int,
                       _c_void_p, _c_int, _c_void_p],
     "rl_gelu_gate": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p],
@@ -224,6 +237,39 @@ def embedding_pos(table: torch.Tensor, pos_table: torch.Tensor, ids: torch.Tenso
     _check(library().rl_embedding_pos(table.data_ptr(), pos_table.data_ptr(), _dt(table), ids.data_ptr(), positions.data_ptr(),
                                       out.data_ptr(), M, d, V, pos_table.shape[0], err_flag.data_ptr(), _stream()),
            "rl_embedding_pos")
+    _count()
+
+
+def embedding_pair(table: torch.Tensor, pair_table: Optional[torch.Tensor], ids: torch.Tensor, positions: torch.Tensor,
+                   slot_of_token: torch.Tensor, cu_seqlens: torch.Tensor, last_token: torch.Tensor, scale: float,
+                   mul_prev: int, mul_cur: int, buckets: int, out: torch.Tensor, err_flag: torch.Tensor) -> None:
+    """out[m, :] = table[ids[m], :] * scale + pair_table[row_m, :] as float32, row_m = (prev_m * mul_prev + ids[m] * mul_cur)
+    mod buckets with prev_m the token in front of token m in its sequence; a sequence's first token takes row
+    ``buckets``.  ``last_token``: the per-slot state view [slots, >= 4 bytes] (uint8) holding, as an int32, the last token
+    each sequence has been fed; read for a step's first token of a sequence that is under way, and updated.
+    ``pair_table`` None: the scaled embedding alone."""
+    _need(table, "table"); _need(ids, "ids", torch.int32); _need(out, "out", torch.float32); _need(err_flag, "err_flag", torch.int32)
+    _need(positions, "positions", torch.int32); _need(slot_of_token, "slot_of_token", torch.int32)
+    _need(cu_seqlens, "cu_seqlens", torch.int32)
+    V, d = table.shape
+    M = ids.numel()
+    assert out.shape == (M, d) and positions.numel() == M and slot_of_token.numel() == M
+    if pair_table is not None:
+        _need(pair_table, "pair_table", table.dtype)
+        assert pair_table.shape == (buckets + 1, d), (pair_table.shape, buckets)
+    sp, ss = _state_args(last_token)
+    _check(library().rl_embedding_pair(table.data_ptr(), _ptr(pair_table), _dt(table), ids.data_ptr(), positions.data_ptr(),
+                                       slot_of_token.data_ptr(), cu_seqlens.data_ptr(), cu_seqlens.numel() - 1, sp, ss,
+                                       float(scale), int(mul_prev), int(mul_cur), int(buckets), out.data_ptr(), M, d, V,
+                                       err_flag.data_ptr(), _stream()), "rl_embedding_pair")
+    _count()
+
+
+def gelu_tanh(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), computed in 32-bit; ``out`` may be ``x``."""
+    _need(x, "x"); _need(out, "out", x.dtype)
+    assert out.shape == x.shape
+    _check(library().rl_gelu_tanh(x.data_ptr(), out.data_ptr(), _dt(x), x.numel(), _stream()), "rl_gelu_tanh")
     _count()
 
 
@@ -458,14 +504,20 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
                    slot_of_token: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
                    num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
                    value_dim: Optional[int] = None, sink: bool = False, gate: Optional[torch.Tensor] = None,
-                   softcap: float = 0.0, keep_first: int = 0) -> None:
+                   softcap: float = 0.0, keep_first: int = 0, chunk: int = 0, values_in_keys: bool = False,
+                   gate_per_head: bool = False) -> None:
     """q: [M, >= H*hd] (a view into the qkv buffer is fine), out: [M, H*vd] where vd is
     ``value_dim`` (default: head_dim), the width of a value head.  ``sink``: the softmax's
     denominator has one more term of score 0 (and no value).  ``gate`` [M, H*vd] (a view is
     fine): the output is multiplied by sigmoid(gate) before it is stored.  ``softcap`` > 0: a score s
     (scale included) becomes softcap * tanh(s / softcap).  ``keep_first``: with a window, positions
-    [0, keep_first) stay visible after the window has passed them."""
+    [0, keep_first) stay visible after the window has passed them.  ``chunk`` > 0 (instead of a window): a query at
+    position p sees positions [p - p % chunk, p].  ``values_in_keys``: the values are the first ``value_dim`` elements
+    of the key rows (``v_pool`` is not read).  ``gate_per_head``: ``gate`` is [M, H], one number a head."""
     vd = head_dim if value_dim is None else value_dim
+    if values_in_keys:
+        assert vd <= head_dim
+        v_pool = k_pool
     _need(q, "q", contiguous=False); _need(k_pool, "k_pool", q.dtype); _need(v_pool, "v_pool", q.dtype)
     _need(out, "out", q.dtype); _need(page_table, "page_table", torch.int32)
     _need(slot_of_token, "slot_of_token", torch.int32); _need(positions, "positions", torch.int32)
@@ -475,13 +527,14 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
     ldg = 0
     if gate is not None:
         _need(gate, "gate", q.dtype, contiguous=False)
-        assert gate.shape == (M, num_heads * vd) and gate.stride(1) == 1
-        ldg = gate.stride(0) if M > 1 else num_heads * vd
-    _check(library().rl_attention_simt_masked(
+        assert gate.shape == (M, num_heads if gate_per_head else num_heads * vd) and gate.stride(1) == 1
+        ldg = gate.stride(0) if M > 1 else gate.shape[1]
+    _check(library().rl_attention_simt_shaped(
         q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), _dt(q), page_table.data_ptr(),
         page_table.shape[1], slot_of_token.data_ptr(), positions.data_ptr(), out.data_ptr(), out.stride(0),
         M, num_heads, num_kv_heads, head_dim, vd, float(scale), int(window), int(bool(sink)), _ptr(gate), ldg,
-        float(softcap or 0.0), int(keep_first or 0), _stream()),
+        float(softcap or 0.0), int(keep_first or 0), int(chunk or 0), head_dim if values_in_keys else 0,
+        int(bool(gate_per_head)), _stream()),
         "rl_attention_simt")
     _count()
 
@@ -566,6 +619,81 @@ def qkv_prepare(u: torch.Tensor, q_out: torch.Tensor, conv_weight: Optional[torc
     _count()
 
 
+def qk_rotate_unit(u: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, slot_of_token: torch.Tensor,
+                   page_table: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, interleaved: bool, unit_eps: Optional[float],
+                   num_heads: int, num_kv_heads: int, head_dim: int, k_pool: Optional[torch.Tensor],
+                   v_pool: Optional[torch.Tensor], value_from_key: bool = False) -> None:
+    """From the projected rows u [M, >= (H + G) * hd] (queries, then keys): every head's first ``rotary_dim`` dimensions
+    are turned by the token's position, then (``unit_eps`` not None) the head is divided by its root mean square;
+    queries to ``q_out`` [M, H*hd] (a view of u is fine), keys to their pages.  ``value_from_key``: the key heads as
+    projected are the values and go to ``v_pool``."""
+    _need(u, "u", contiguous=False); _need(q_out, "q_out", u.dtype, contiguous=False); _need(positions, "positions", torch.int32)
+    _need(inv_freq, "inv_freq", torch.float32)
+    M = u.shape[0]
+    assert u.stride(1) == 1 and q_out.stride(1) == 1 and u.shape[1] >= (num_heads + num_kv_heads) * head_dim
+    assert q_out.shape[1] >= num_heads * head_dim and inv_freq.numel() >= max(1, rotary_dim // 2)
+    max_pages = 0
+    if k_pool is not None:
+        _need(k_pool, "k_pool", u.dtype); _need(slot_of_token, "slot_of_token", torch.int32); _need(page_table, "page_table", torch.int32)
+        assert k_pool.shape[1:] == (num_kv_heads, PAGE_SIZE, head_dim), k_pool.shape
+        if value_from_key:
+            _need(v_pool, "v_pool", u.dtype)
+            assert v_pool.shape == k_pool.shape
+        max_pages = page_table.shape[1]
+    ldu = u.stride(0) if M > 1 else u.shape[1]
+    ldq = q_out.stride(0) if M > 1 else q_out.shape[1]
+    _check(library().rl_qk_rotate_unit(u.data_ptr(), ldu, q_out.data_ptr(), ldq, _dt(u), positions.data_ptr(), _ptr(slot_of_token),
+                                       _ptr(page_table), max_pages, inv_freq.data_ptr(), int(rotary_dim), int(bool(interleaved)),
+                                       int(unit_eps is not None), float(unit_eps or 0.0), M, num_heads, num_kv_heads, head_dim,
+                                       int(bool(value_from_key)), _ptr(k_pool), _ptr(v_pool) if value_from_key else None, _stream()),
+           "rl_qk_rotate_unit")
+    _count()
+
+
+def latent_prepare(u: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, q_weight: Optional[torch.Tensor],
+                   kv_weight: torch.Tensor, eps: float, cq: Optional[torch.Tensor], positions: torch.Tensor,
+                   slot_of_token: torch.Tensor, page_table: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int,
+                   interleaved: bool, k_pool: Optional[torch.Tensor]) -> None:
+    """u [M, >= q_rank + kv_rank + rot_dim] = [query latent | key/value latent | shared rotary key] as projected:
+    cq = rms_norm(query latent) * q_weight; the token's key row [rms_norm(key/value latent) * kv_weight | turned rotary
+    key] goes to its page of ``k_pool`` [pages, 1, PAGE_SIZE, kv_rank + rot_dim]."""
+    _need(u, "u", contiguous=False); _need(positions, "positions", torch.int32); _need(inv_freq, "inv_freq", torch.float32)
+    _need(kv_weight, "kv_weight", torch.float32)
+    M = u.shape[0]
+    assert u.stride(1) == 1 and u.shape[1] >= q_rank + kv_rank + rot_dim and kv_weight.numel() == kv_rank
+    ldc = 0
+    if q_rank:
+        _need(q_weight, "q_weight", torch.float32); _need(cq, "cq", u.dtype, contiguous=False)
+        assert q_weight.numel() == q_rank and cq.shape == (M, q_rank) and cq.stride(1) == 1
+        ldc = cq.stride(0) if M > 1 else q_rank
+    max_pages = 0
+    if k_pool is not None:
+        _need(k_pool, "k_pool", u.dtype); _need(slot_of_token, "slot_of_token", torch.int32); _need(page_table, "page_table", torch.int32)
+        assert k_pool.shape[1:] == (1, PAGE_SIZE, kv_rank + rot_dim), k_pool.shape
+        max_pages = page_table.shape[1]
+    ldu = u.stride(0) if M > 1 else u.shape[1]
+    _check(library().rl_latent_prepare(u.data_ptr(), ldu, _dt(u), int(q_rank), int(kv_rank), int(rot_dim), _ptr(q_weight),
+                                       kv_weight.data_ptr(), float(eps), _ptr(cq) if q_rank else None, ldc, positions.data_ptr(),
+                                       _ptr(slot_of_token), _ptr(page_table), max_pages, inv_freq.data_ptr(), int(rotary_dim),
+                                       int(bool(interleaved)), M, _ptr(k_pool), _stream()), "rl_latent_prepare")
+    _count()
+
+
+def latent_query(q: torch.Tensor, out: torch.Tensor, num_heads: int, head_dim: int, rot_dim: int, latent_dim: int,
+                 positions: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, interleaved: bool) -> None:
+    """q [M, H * (hd + rd)] (a head: [plain | rotary]); the turned rotary parts go behind the ``latent_dim`` columns of
+    each head of ``out`` [M, H * (latent_dim + rd)]."""
+    _need(q, "q", contiguous=False); _need(out, "out", q.dtype); _need(positions, "positions", torch.int32)
+    _need(inv_freq, "inv_freq", torch.float32)
+    M = q.shape[0]
+    assert q.stride(1) == 1 and q.shape[1] == num_heads * (head_dim + rot_dim) and out.shape == (M, num_heads * (latent_dim + rot_dim))
+    ldq = q.stride(0) if M > 1 else q.shape[1]
+    _check(library().rl_latent_query(q.data_ptr(), ldq, _dt(q), num_heads, head_dim, rot_dim, positions.data_ptr(),
+                                     inv_freq.data_ptr(), int(rotary_dim), int(bool(interleaved)), out.data_ptr(), out.stride(0),
+                                     latent_dim, M, _stream()), "rl_latent_query")
+    _count()
+
+
 def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, state: torch.Tensor,
                 cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, num_heads: int, heads_per_group: int, dk: int, dv: int,
                 rate: torch.Tensor, dt_raw: Optional[torch.Tensor] = None, dt_bias: Optional[torch.Tensor] = None,
@@ -601,9 +729,9 @@ def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Te
 
 
 def norm_add(x: torch.Tensor, y0: torch.Tensor, s0: float, y1: Optional[torch.Tensor], s1: float, weight: torch.Tensor, eps: float,
-             x_bf16: Optional[torch.Tensor] = None) -> None:
-    """x += rms_norm(s0 * y0 + s1 * y1) * weight, all float32 [M, d] (``y1`` may be ``None``); ``x_bf16``: also
-    leave the new x there, rounded."""
+             x_bf16: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> None:
+    """x += out_scale * rms_norm(s0 * y0 + s1 * y1) * weight, all float32 [M, d] (``y1`` may be ``None``); ``x_bf16``:
+    also leave the new x there, rounded."""
     _need(x, "x", torch.float32); _need(y0, "y0", torch.float32); _need(weight, "weight", torch.float32)
     M, d = x.shape
     assert y0.shape == (M, d) and weight.numel() == d
@@ -613,8 +741,8 @@ def norm_add(x: torch.Tensor, y0: torch.Tensor, s0: float, y1: Optional[torch.Te
     if x_bf16 is not None:
         _need(x_bf16, "x_bf16", torch.bfloat16)
         assert x_bf16.shape == (M, d)
-    _check(library().rl_norm_add(x.data_ptr(), y0.data_ptr(), float(s0), _ptr(y1), float(s1), weight.data_ptr(), float(eps), M, d,
-                                 _ptr(x_bf16), _stream()), "rl_norm_add")
+    _check(library().rl_norm_add(x.data_ptr(), y0.data_ptr(), float(s0), _ptr(y1), float(s1), weight.data_ptr(), float(eps),
+                                 float(out_scale), M, d, _ptr(x_bf16), _stream()), "rl_norm_add")
     _count()
 
 
@@ -1151,13 +1279,24 @@ def attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
               step, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
               window: int = 0, value_dim: Optional[int] = None, sink: bool = False,
-              gate: Optional[torch.Tensor] = None, softcap: float = 0.0, keep_first: int = 0) -> None:
+              gate: Optional[torch.Tensor] = None, softcap: float = 0.0, keep_first: int = 0, chunk: int = 0,
+              values_in_keys: bool = False, gate_per_head: bool = False) -> None:
     """Attention of the step's tokens over the cache; picks the kernel for the
     dtype and the shape of the step.  ``step`` carries positions, slots and
     sequence boundaries (engine.step.StepState).  Value heads of another width than the
     key heads (``value_dim``) run on the any-shape kernel; the tensor-core kernels take
     one width for both.  ``sink``: one more term of score 0 in the softmax's denominator.
-    ``gate`` [M, H*vd]: the output is multiplied by sigmoid(gate)."""
+    ``gate`` [M, H*vd]: the output is multiplied by sigmoid(gate) (``gate_per_head``: [M, H], one number a head).
+    ``chunk`` > 0 instead of a window: a query sees the positions of its own block of ``chunk`` positions up to
+    itself.  ``values_in_keys``: the values are the front part of the key rows (any-shape kernel)."""
+    if chunk and window:
+        raise KernelError("a chunked mask and a sliding window exclude one another")
+    if values_in_keys or gate_per_head or chunk:
+        attention_simt(q, k_pool, v_pool, page_table, step.slot_of_token, step.positions, out,
+                       num_heads, num_kv_heads, head_dim, scale, window, value_dim=value_dim, sink=sink, gate=gate,
+                       softcap=softcap, keep_first=keep_first, chunk=chunk, values_in_keys=values_in_keys,
+                       gate_per_head=gate_per_head)
+        return
     masked = bool(softcap or (keep_first and window))
     tc_prefill = (not step.is_decode and attention_prefill_tc_supported(q.dtype, num_heads, num_kv_heads, head_dim)
                   and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0

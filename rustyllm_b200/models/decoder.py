@@ -76,6 +76,13 @@ class DecoderModel:
             else:
                 self.run_entry.append((latest_entry_of_layer[src], False))
 
+        # an embedding with per-sequence state of its own (say, the last token it was fed) gets an entry behind the layers'
+        self.embedding_entry: Optional[int] = None
+        need = self.embedding.state_need() if hasattr(self.embedding, "state_need") else None
+        if need is not None:
+            self.entry_needs.append((None, need))
+            self.embedding_entry = len(self.entry_needs) - 1
+
         self._params: Dict[str, Tuple[Part, str, ParamSpec]] = {}
         _collect_params("embedding", self.embedding, self._params)
         for i, b in enumerate(self.blocks):
@@ -146,7 +153,10 @@ class DecoderModel:
         nat = self.native_for(cache)
         if nat is not None:
             return nat.forward(step)
-        x = self.embedding.forward(step)
+        if self.embedding_entry is not None:
+            x = self.embedding.forward(step, cache.state_entry(self.embedding_entry))
+        else:
+            x = self.embedding.forward(step)
         embedded = None
         if self._keep_embedded:      # the stream as the embedding leaves it, for parts that add it again later
             embedded = torch.empty_like(x)

@@ -13,7 +13,10 @@ convolution over time on every channel of q, k and v, directly behind the projec
 last taps - 1 projected rows of a sequence are per-sequence state); an RMS norm of every query and key head
 with one weight vector for all heads, before the rotation (``names["q_norm"]``, ``names["k_norm"]``,
 ``qk_norm_eps``); scores squashed to softcap * tanh(s / softcap) (``softcap``); first positions that stay
-visible behind a window (``keep_first``).  Here Wq, Wk, Wv are one matrix [(H + 2G) hd x d] so that one product
+visible behind a window (``keep_first``); a chunked mask instead of a window (``chunk`` = C: a query at position i
+sees j <= i with i // C == j // C, blocks counted from the sequence's start); query and key heads divided by their
+root mean square after the rotation, without a weight (``unit_qk_eps``); values that are the keys as projected,
+before rotation and norm, with no value projection (``value_from_key``).  Here Wq, Wk, Wv are one matrix [(H + 2G) hd x d] so that one product
 serves all three, rotation and cache write are one kernel, and all tokens of the
 step (several sequences, prompt or single tokens) run together.
 """
@@ -39,7 +42,8 @@ class GQAttention(Mixer):
                  window: Optional[int] = None, value_dim: Optional[int] = None,
                  scale: Optional[float] = None, sink: bool = False, conv_taps: int = 0,
                  qk_norm_eps: Optional[float] = None, softcap: Optional[float] = None, keep_first: int = 0,
-                 bias_o: Optional[bool] = None):
+                 bias_o: Optional[bool] = None, chunk: Optional[int] = None, unit_qk_eps: Optional[float] = None,
+                 value_from_key: bool = False):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are no multiple of {num_kv_heads} KV heads")
         if head_dim % 2 or not (0 < head_dim <= 256):
@@ -80,12 +84,22 @@ class GQAttention(Mixer):
             raise ValueError("an output gate together with a convolution or head norms is not built")
         self.channels = (num_heads + num_kv_heads) * head_dim + num_kv_heads * vd
         self.conv_w = self.q_norm_w = self.k_norm_w = None
+        if chunk is not None and (chunk <= 0 or window is not None):
+            raise ValueError("chunk must be > 0 or None, and excludes a window")
+        self.chunk = chunk
+        self.unit_qk_eps = None if unit_qk_eps is None else float(unit_qk_eps)
+        self.value_from_key = bool(value_from_key)
+        if self.value_from_key and vd != head_dim:
+            raise ValueError(f"values that are the keys need value_dim = head_dim, got {vd} and {head_dim}")
+        if (self.value_from_key or self.unit_qk_eps is not None) and (bias or self.conv_taps or self.qk_norm):
+            raise ValueError("unit-size heads or values from keys together with biases, a convolution or weighted head norms are not built")
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         d, H, G, hd, vd, n = self.d, self.H, self.G, self.hd, self.vd, self.names
         sfx = n.get("suffix", ".weight")     # what follows a projection's name in the checkpoint
-        qkv = (ParamSource(n["q"] + sfx, (H * hd, d)), ParamSource(n["k"] + sfx, (G * hd, d)),
-               ParamSource(n["v"] + sfx, (G * vd, d)))
+        qkv = (ParamSource(n["q"] + sfx, (H * hd, d)), ParamSource(n["k"] + sfx, (G * hd, d)))
+        if not self.value_from_key:
+            qkv += (ParamSource(n["v"] + sfx, (G * vd, d)),)
         if self.gated:
             qkv += (ParamSource(n["g"] + sfx, (H * vd, d)),)
         specs = {"wqkv": ParamSpec(qkv), "wo": ParamSpec((ParamSource(n["o"] + sfx, (d, H * vd)),))}
@@ -107,7 +121,7 @@ class GQAttention(Mixer):
         return specs
 
     def kv_need(self) -> KVNeed:
-        return KVNeed(self.G, self.hd, self.window, None if self.vd == self.hd else self.vd, self.keep_first)
+        return KVNeed(self.G, self.hd, self.window, None if self.vd == self.hd else self.vd, self.keep_first, self.chunk)
 
     def state_need(self) -> Optional[StateNeed]:
         # the last taps - 1 projected rows of a sequence, float32
@@ -129,7 +143,7 @@ class GQAttention(Mixer):
         H, G, hd, vd = self.H, self.G, self.hd, self.vd
         M = xn.shape[0]
         dt = xn.dtype
-        n_qkv = (H + G) * hd + G * vd
+        n_qkv = (H + G) * hd + (0 if self.value_from_key else G * vd)
         qkv = torch.empty((M, n_qkv + (H * vd if self.gated else 0)), dtype=dt, device=xn.device)
         group, layer = cache.kv_group, cache.kv_layer
         k_pool, v_pool = group.k_pool(layer), group.v_pool(layer)
@@ -138,7 +152,15 @@ class GQAttention(Mixer):
         magnitude = getattr(pos, "magnitude", 1.0)      # a position kind of its own need not know the attribute
         prepared = self.conv_taps or self.qk_norm or magnitude != 1.0
         q = qkv
-        if prepared:
+        if self.value_from_key or self.unit_qk_eps is not None:
+            # rotation first, then heads of unit size; the keys as projected are the values: one kernel behind the product
+            linear(xn, self.wqkv, qkv, OUT_SAME, self.bqkv)
+            if not self.value_from_key:
+                raise K.KernelError("unit-size heads with a value projection of their own are not built")
+            K.qk_rotate_unit(qkv, qkv, step.positions, step.slot_of_token, group.page_table, pos.inv_freq, pos.rotary_dim,
+                             pos.interleaved, self.unit_qk_eps, H, G, hd, k_pool if cache.writes else None,
+                             v_pool if cache.writes else None, value_from_key=True)
+        elif prepared:
             # convolution, head norms, rotation and the cache write in one kernel behind the product
             linear(xn, self.wqkv, qkv, OUT_SAME, self.bqkv)
             q = torch.empty((M, H * hd), dtype=dt, device=xn.device)
@@ -165,5 +187,5 @@ class GQAttention(Mixer):
         attn = torch.empty((M, H * vd), dtype=dt, device=xn.device)
         K.attention(q, k_pool, v_pool, group.page_table, step, attn, H, G, hd, self.scale,
                     self.window or 0, value_dim=vd, sink=self.sink, gate=qkv[:, n_qkv:] if self.gated else None,
-                    softcap=self.softcap, keep_first=self.keep_first)
+                    softcap=self.softcap, keep_first=self.keep_first, chunk=self.chunk or 0)
         return linear(attn, self.wo, residual, _out_mode, self.bo, then_norm=then_norm)

@@ -59,8 +59,9 @@ class PreNormBlock(Block):
 class PostNormBlock(Block):
     """A layer whose sublayers read the stream itself and whose norms sit on what they return:
 
-        x += norm1(mixer(x));  x += norm2(feed_forward(x));  then, where the layer has one, ``after`` (a part of
-        role "inject", e.g. a per-token side input) changes x once more.
+        x += m norm1(mixer(x));  x += m norm2(feed_forward(x))  (m = ``residual_scale``, 1 unless the model says
+        otherwise);  then, where the layer has one, ``after`` (a part of role "inject", e.g. a per-token side input)
+        changes x once more.
 
     The stream is float32; a bfloat16 run hands the sublayers its rounding, which the kernel that adds a normed
     output into the stream leaves behind for the next reader.  A mixer that offers ``forward_out`` returns its
@@ -69,9 +70,10 @@ class PostNormBlock(Block):
     """
 
     def __init__(self, runtime: Runtime, mixer: Mixer, mixer_norm: Norm, feed_forward: FeedForward,
-                 feed_forward_norm: Norm, after=None):
+                 feed_forward_norm: Norm, after=None, residual_scale: float = 1.0):
         from .registry import build_part
         self.runtime = runtime
+        self.residual_scale = float(residual_scale)     # x += residual_scale * norm(sublayer(x)): a constant of the model
         self.mixer, self.mixer_norm = mixer, mixer_norm
         self.feed_forward, self.feed_forward_norm = feed_forward, feed_forward_norm
         self.after = build_part("inject", after, runtime) if after is not None else None
@@ -97,7 +99,7 @@ class PostNormBlock(Block):
         return h
 
     def _join(self, x, terms, norm):
-        """x += norm(sum of factor * tensor); returns the new x's bfloat16 rounding in a bfloat16 run."""
+        """x += residual_scale * norm(sum of factor * tensor); returns the new x's bfloat16 rounding in a bfloat16 run."""
         from .. import kernels as K
         if len(terms) > 2:
             raise K.KernelError("more than two terms under one norm are not built")
@@ -105,7 +107,7 @@ class PostNormBlock(Block):
         if self.runtime.compute_dtype == torch.bfloat16:
             rounded = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
         (y0, s0), (y1, s1) = terms[0], (terms[1] if len(terms) > 1 else (None, 0.0))
-        K.norm_add(x, y0, s0, y1, s1, norm.weight, norm.eps, rounded)
+        K.norm_add(x, y0, s0, y1, s1, norm.weight, norm.eps, rounded, out_scale=self.residual_scale)
         return rounded
 
     def forward(self, x: torch.Tensor, step, cache, pending=None, next_norm=None):

@@ -12,6 +12,7 @@ from typing import Dict, Optional
 import torch
 
 from .. import kernels as K
+from ..cache.sequence_cache import StateNeed
 from ..config.spec import ParamSource, ParamSpec
 from .base import Part, Runtime
 from .linear import OUT_F32, linear
@@ -60,6 +61,40 @@ class TokenPositionEmbedding(TokenEmbedding):
         tokens = step.tokens
         x = torch.empty((tokens.numel(), self.d), dtype=torch.float32, device=tokens.device)
         K.embedding_pos(self.weight, self.positions, tokens, step.positions, x, self.bad_token)
+        return x
+
+
+@register("embedding", "scaled_pair_embedding")
+class ScaledPairEmbedding(TokenEmbedding):
+    """x = scale * E[token] + P[(mul_prev * previous token + mul_cur * token) mod buckets], summed in 32-bit; a
+    sequence's first token takes row ``buckets`` of P, which has buckets + 1 rows.  The previous token belongs to
+    the sequence's state: an int32 a slot in the cache's state area (``state_need``), read where a step's first
+    token of a sequence continues one that is under way, and left behind by every step.  Without ``buckets``:
+    the scaled token embedding alone."""
+
+    def __init__(self, runtime: Runtime, vocab_size: int, hidden_size: int, name: str, scale: float = 1.0,
+                 buckets: Optional[int] = None, mul_prev: int = 0, mul_cur: int = 0, pair_name: Optional[str] = None):
+        super().__init__(runtime, vocab_size, hidden_size, name)
+        if buckets is not None and (buckets <= 0 or mul_prev < 0 or mul_cur < 0 or not pair_name):
+            raise ValueError("a pair table needs buckets > 0, multipliers >= 0 and a tensor name")
+        self.scale = float(scale)
+        self.buckets, self.mul_prev, self.mul_cur, self.pair_name = buckets, int(mul_prev), int(mul_cur), pair_name
+        self.pairs: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        specs = super().param_specs()
+        if self.buckets is not None:
+            specs["pairs"] = ParamSpec((ParamSource(self.pair_name, (self.buckets + 1, self.d)),), role="table")
+        return specs
+
+    def state_need(self) -> StateNeed:
+        return StateNeed(4)        # the last token the sequence was fed
+
+    def forward(self, step, state: torch.Tensor) -> torch.Tensor:
+        tokens = step.tokens
+        x = torch.empty((tokens.numel(), self.d), dtype=torch.float32, device=tokens.device)
+        K.embedding_pair(self.weight, self.pairs, tokens, step.positions, step.slot_of_token, step.cu_seqlens, state, self.scale,
+                         self.mul_prev, self.mul_cur, self.buckets or 1, x, self.bad_token)
         return x
 
 

@@ -71,6 +71,38 @@ class GatedMLP(FeedForward):
         return linear(h, self.wdown, residual, OUT_ADD_F32, self.bdown, then_norm=then_norm)
 
 
+@register_feed_forward("dense_mlp")
+class DenseMLP(FeedForward):
+    """Feed-forward without a gate: Wdown act(Wup xn), act the tanh form of gelu,
+    0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), computed in 32-bit from the product's output."""
+
+    def __init__(self, runtime: Runtime, hidden_size: int, intermediate_size: int, names: Dict[str, str],
+                 activation: str = "gelu_tanh"):
+        if activation != "gelu_tanh":
+            raise ValueError(f"activation {activation!r} is not supported; known: 'gelu_tanh'")
+        self.runtime = runtime
+        self.d, self.I = hidden_size, intermediate_size
+        self.names = names
+        self.wup = self.wdown = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        d, I, n = self.d, self.I, self.names
+        sfx = n.get("suffix", ".weight")
+        return {"wup": ParamSpec((ParamSource(n["up"] + sfx, (I, d)),)),
+                "wdown": ParamSpec((ParamSource(n["down"] + sfx, (d, I)),))}
+
+    def forward_out(self, xn, step):
+        y = torch.empty((xn.shape[0], self.d), dtype=torch.float32, device=xn.device)
+        self.forward(xn, y, step, _out_mode=K.OUT_F32)
+        return [(y, 1.0)]
+
+    def forward(self, xn, residual: torch.Tensor, step, _out_mode=OUT_ADD_F32):
+        h = torch.empty((xn.shape[0], self.I), dtype=xn.dtype, device=xn.device)
+        linear(xn, self.wup, h, OUT_SAME)
+        K.gelu_tanh(h, h)
+        return linear(h, self.wdown, residual, _out_mode)
+
+
 @register_feed_forward("none")
 class NoFeedForward(FeedForward):
     """A layer without a feed-forward: the block skips its second half."""

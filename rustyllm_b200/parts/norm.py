@@ -3,6 +3,10 @@
 SimonWaldherr/RustyLLM src/model.rs:5429-5437 (``rms_norm_into``): no mean subtraction, no
 bias, the weight used as it is (no ``1 + w``).  Used before the mixer, before the
 feed-forward and before the head (src/model.rs:7205, 7321, 7351).
+
+``offset``: a design that stores its norm weights around zero and multiplies by ``offset + w``
+(``offset`` = 1) says so; the sum is formed once, in float32, when the weight is bound, and every
+kernel sees an ordinary weight.
 """
 from __future__ import annotations
 
@@ -18,15 +22,24 @@ from .registry import register_norm
 
 @register_norm("rms_norm")
 class RMSNorm(Norm):
-    def __init__(self, runtime: Runtime, size: int, eps: float, name: str):
+    def __init__(self, runtime: Runtime, size: int, eps: float, name: str, offset: float = 0.0):
         self.runtime = runtime
         self.size = size
         self.eps = float(eps)
         self.name = name
+        self.offset = float(offset)
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((ParamSource(self.name, (self.size,)),), role="vector", init="ones")}
+        # a weight stored around zero is drawn around zero in the random-weights mode
+        return {"weight": ParamSpec((ParamSource(self.name, (self.size,)),), role="vector",
+                                    init="normal" if self.offset else "ones")}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        w = tensors.get("weight")
+        if w is not None and self.offset:
+            tensors = dict(tensors, weight=w.to(torch.float32) + self.offset)
+        super().bind(tensors)
 
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = x.shape[0] if rows is None else rows.numel()
