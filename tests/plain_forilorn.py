@@ -67,9 +67,13 @@ def gelu_tanh(z: torch.Tensor) -> torch.Tensor:
     return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
 
 
-def rotate_pairs(x: torch.Tensor, positions: Sequence[int], dims: int, base: float) -> torch.Tensor:
-    """x [T, ..., width]: neighbours (2i, 2i + 1) among the first ``dims`` turn by position * base^(-2i/dims)."""
+def rotate_pairs(x: torch.Tensor, positions: Sequence[int], rot: Optional[dict]) -> torch.Tensor:
+    """x [T, ..., width]: neighbours (2i, 2i + 1) among the first ``dims`` turn by position * base^(-2i/dims);
+    ``rot`` = {"dims", "base"} or None (nothing turns)."""
     out = x.clone()
+    if not rot:
+        return out
+    dims, base = rot["dims"], rot["base"]
     for t, p in enumerate(positions):
         for i in range(dims // 2):
             a = p * base ** (-2.0 * i / dims)
@@ -88,22 +92,26 @@ def softmax_rows(scores: torch.Tensor, visible: torch.Tensor) -> torch.Tensor:
     return e / e.sum(dim=-1, keepdim=True)
 
 
-def chunk_mask(T: int, size: int) -> torch.Tensor:
+def chunk_mask(T: int, size: Optional[int]) -> torch.Tensor:
     i = torch.arange(T).unsqueeze(1)
     j = torch.arange(T).unsqueeze(0)
+    if size is None:
+        return j <= i
     return (j <= i) & (torch.div(i, size, rounding_mode="floor") == torch.div(j, size, rounding_mode="floor"))
 
 
-def window_mask(T: int, size: int) -> torch.Tensor:
+def window_mask(T: int, size: Optional[int]) -> torch.Tensor:
     i = torch.arange(T).unsqueeze(1)
     j = torch.arange(T).unsqueeze(0)
+    if size is None:
+        return j <= i
     return (j <= i) & (i - j < size)
 
 
 # --------------------------------------------------------------------------- the parts
 def embed(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -> torch.Tensor:
-    e = cfg["embedding"]
-    x = w["embed"][list(tokens)] * e["scale"]
+    e = cfg.get("embedding") or {}
+    x = w["embed"][list(tokens)] * e.get("scale", 1.0)
     bg = e.get("bigram")
     if bg:
         rows = [bg["buckets"]] + [(tokens[t - 1] * bg["mul_prev"] + tokens[t] * bg["mul_cur"]) % bg["buckets"]
@@ -119,9 +127,9 @@ def attention_mixer(m: dict, w: Dict[str, torch.Tensor], p: str, h: torch.Tensor
     k = (h @ w[p + "k"].T).reshape(T, G, hd)
     v = k.clone()                                        # the values are the keys as projected
     pos = list(range(T))
-    q = unit_rms(rotate_pairs(q, pos, m["rot"]["dims"], m["rot"]["base"]), eps)
-    k = unit_rms(rotate_pairs(k, pos, m["rot"]["dims"], m["rot"]["base"]), eps)
-    visible = chunk_mask(T, m["mask"]["size"])
+    q = unit_rms(rotate_pairs(q, pos, m.get("rot")), eps)
+    k = unit_rms(rotate_pairs(k, pos, m.get("rot")), eps)
+    visible = chunk_mask(T, (m.get("mask") or {}).get("size"))
     heads = []
     for a in range(H):
         g = a // (H // G)
@@ -137,14 +145,14 @@ def latent_mixer(m: dict, w: Dict[str, torch.Tensor], p: str, h: torch.Tensor, e
     pos = list(range(T))
     cq = unit_rms(h @ w[p + "dq"].T, eps) * w[p + "dq.norm"]
     q = (cq @ w[p + "uq"].T).reshape(T, H, hd + rd)
-    q_plain, q_rot = q[..., :hd], rotate_pairs(q[..., hd:], pos, m["rot"]["dims"], m["rot"]["base"])
+    q_plain, q_rot = q[..., :hd], rotate_pairs(q[..., hd:], pos, m.get("rot"))
     ckr = h @ w[p + "dkv"].T
     c = unit_rms(ckr[:, :r], eps) * w[p + "dkv.norm"]
-    kr = rotate_pairs(ckr[:, r:], pos, m["rot"]["dims"], m["rot"]["base"])          # [T, rd], one for all heads
+    kr = rotate_pairs(ckr[:, r:], pos, m.get("rot"))          # [T, rd], one for all heads
     k = (c @ w[p + "uk"].T).reshape(T, H, hd)
     v = (c @ w[p + "uv"].T).reshape(T, H, vd)
     gate = sigmoid(h @ w[p + "g"].T)                     # [T, H]: one number a head
-    visible = window_mask(T, m["mask"]["size"])
+    visible = window_mask(T, (m.get("mask") or {}).get("size"))
     heads = []
     for a in range(H):
         s = (q_plain[:, a] @ k[:, a].T + q_rot[:, a] @ kr.T) * m["scale"]
@@ -159,7 +167,7 @@ def dense_ff(w: Dict[str, torch.Tensor], p: str, h: torch.Tensor) -> torch.Tenso
 # --------------------------------------------------------------------------- the model
 def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], return_layers: bool = False):
     """Logits [T, vocab] of one whole sequence (and the stream after every layer, [layers, T, width])."""
-    eps, mult = cfg["norm"]["eps"], cfg["residual_mult"]
+    eps, mult = cfg["norm"]["eps"], cfg.get("residual_mult", 1.0)
     x = embed(cfg, w, tokens)
     after = []
     for i, layer in enumerate(cfg["layers"]):
