@@ -1,4 +1,4 @@
-"""Prompt and single-token throughput of the Mosurax and Mogutar designs beside the Llama decoder at equal layer sizes
+"""Prompt and single-token throughput of the Mosurax, Mogutar and Forilorn designs beside the Llama decoder at equal layer sizes
 (random bfloat16 weights, synthetic tokens): ``python bench.py --designs`` or
 ``python -m rustyllm_b200.bench_designs [--size NAME] [--steps K] [--warmup W]``.
 
@@ -12,6 +12,11 @@ uses together with the shared one are as wide as the dense feed-forward), vocabu
                  window of 1,024 with 8 kept tokens) beside a selective state-space mixer of the model's width, two in
                  four with linear attention with decay; every feed-forward 16 experts in 4 groups (2 kept), 4 a token,
                  each a quarter of the dense width; a per-layer token input of 256 columns
+  forilorn       post-norm layers with a scaled stream; three in four with grouped-query attention whose values are its
+                 keys (no value projection), rotated neighbours, unit-size q and k heads, blocks of 1,024 positions as the
+                 mask and an output gate an element; one in four with attention through latents (queries 3/8 of the
+                 width, keys and values 1/4 of it plus a rotary key part of 64 for all heads, a window of 1,024, a gate
+                 a head); dense gelu feed-forwards; a hashed pair table of 65,536 rows beside the embedding; tied head
 ``--kernels`` times the Mogutar design's own kernels alone at the sizes of a layer (a JSON line a kernel, with the
 bytes it must move and their share of the measured copy bandwidth).
 Measured with CUDA events after warm-up: one prompt of ``prompt`` tokens as one step; then single-token steps of
@@ -34,6 +39,7 @@ SIZES = {
                   experts=16, top=3, expert_ff=3584, shared_ff=3584),
 }
 MAX_POSITIONS = 4096
+MODELS = ("llama", "mosurax-dense", "mosurax-moe", "mogutar", "forilorn")
 
 
 def llama_config(s: dict) -> dict:
@@ -72,6 +78,18 @@ def mogutar_config(s: dict, window: int = 1024) -> dict:
                            "mlp": dict(mlp)})
     return {"architecture": "Mogutar", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5}, "token_side": {"dim": 256},
             "layers": layers}
+
+
+def forilorn_config(s: dict, window: int = 1024) -> dict:
+    d, H, hd = s["width"], s["heads"], s["dim"]
+    plain = {"heads": H, "kv_heads": s["kv_heads"], "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": window},
+             "rot": {"base": 10000.0, "dims": hd}}
+    lat = {"heads": H, "dim": hd, "rot_dim": 64, "vdim": hd, "q_rank": 3 * d // 8, "kv_rank": d // 4, "scale": (hd + 64) ** -0.5,
+           "mask": {"size": window}, "rot": {"base": 10000.0, "dims": 64}}
+    layers = [{"type": "latent_attention" if i % 4 == 2 else "attention", "mixer": dict(lat if i % 4 == 2 else plain),
+               "mlp": {"kind": "dense", "ff": s["ff"]}} for i in range(s["layers"])]
+    return {"architecture": "Forilorn", "vocab": s["vocab"], "width": d, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "embedding": {"scale": d ** 0.5, "bigram": {"buckets": 65536, "mul_prev": 31, "mul_cur": 17}}, "layers": layers}
 
 
 def measure(config: dict, prompt: int, batches: List[int], context: int, steps: int, warmup: int) -> Dict[str, float]:
@@ -128,14 +146,15 @@ def measure(config: dict, prompt: int, batches: List[int], context: int, steps: 
 
 
 def run(sizes: List[str], prompt: int = 2048, batches=(8, 64), context: int = 1024, steps: int = 32, warmup: int = 8,
-        window: int = 0, models=("llama", "mosurax-dense", "mosurax-moe", "mogutar")) -> List[dict]:
+        window: int = 0, models=None) -> List[dict]:
     lines = []
+    models = tuple(models or MODELS)
     for name in sizes:
         s = SIZES[name]
         got = {}
         for model in models:
             cfg = llama_config(s) if model == "llama" else mogutar_config(s, window or 1024) if model == "mogutar" \
-                else mosurax_config(s, model == "mosurax-moe", window or None)
+                else forilorn_config(s, window or 1024) if model == "forilorn" else mosurax_config(s, model == "mosurax-moe", window or None)
             got[model] = measure(cfg, prompt, list(batches), context, steps, warmup)
             line = {"size": name, "model": model, "prompt_tokens": prompt, "context": context, "window": window or None,
                     "dtype": "bf16", "data": "synthetic", **got[model]}
@@ -261,11 +280,177 @@ def kernel_times(sizes: List[str], prompt: int = 2048, batch: int = 64, runs: in
     return lines
 
 
+def forilorn_kernel_times(sizes: List[str], prompt: int = 2048, batch: int = 64, context: int = 1024, mask: int = 1024,
+                          runs: int = 20) -> List[dict]:
+    """The Forilorn design's kernels alone beside the like kernel of the Mosurax design, bfloat16, at a layer's sizes:
+    ``prompt`` tokens of one sequence, and one token of each of ``batch`` sequences that hold ``context`` tokens.  A
+    row gives the bytes the kernel must move and the operations it must do, the time both would take at the measured
+    copy bandwidth and matrix throughput, and the larger of the two over the measured time (``of_roofline``)."""
+    import json as _json
+    import os
+    import torch
+    from . import kernels as K
+    from .cache.sequence_cache import KVNeed, SequenceCache
+    from .engine.step import StepState
+    peaks = {}
+    try:
+        with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")) as f:
+            peaks = _json.load(f)
+    except OSError:
+        pass
+    gbs, tflops = float(peaks.get("hbm_gbs", 6650.0)), float(peaks.get("bf16_tflops", 1590.0))
+    dev, bf = torch.device("cuda:0"), torch.bfloat16
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(runs):
+            flush.zero_()                      # a buffer larger than L2 between runs
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return sorted(ts)[len(ts) // 2] * 1e3   # us
+
+    lines = []
+
+    def report(size, design, kernel, shape, us, nbytes, flops=0.0):
+        floor = max(nbytes / (gbs * 1e3), flops / (tflops * 1e6))        # us
+        line = {"size": size, "design": design, "kernel": kernel, "shape": shape, "us": round(us, 2), "gb": round(nbytes / 1e9, 4),
+                "gflop": round(flops / 1e9, 3), "floor_us": round(floor, 2), "of_roofline": round(floor / us, 3),
+                "bound": "bandwidth" if nbytes / (gbs * 1e3) >= flops / (tflops * 1e6) else "matrix"}
+        print(_json.dumps(line), flush=True)
+        lines.append(line)
+
+    def steps_for(cache, B, held, cnt):
+        """B sequences that hold ``held`` tokens and bring ``cnt`` more: the cache prepared, and the step's description."""
+        slots = [cache.alloc_slot() for _ in range(B)]
+        if held:
+            cache.prepare(slots, [held] * B); cache.commit(slots, [held] * B)
+        cache.prepare(slots, [cnt] * B)
+        M = B * cnt
+        return StepState(M, B, i32([0] * M), i32([held + t for _ in range(B) for t in range(cnt)]),
+                         i32([s for s in slots for _ in range(cnt)]), i32([cnt * b for b in range(B + 1)]), i32(slots),
+                         i32([held + cnt] * B), i32([]), [cnt] * B, [held + cnt] * B, cnt, held + cnt, cnt == 1)
+
+    for name in sizes:
+        s = SIZES[name]
+        d, H, G, hd, ff = s["width"], s["heads"], s["kv_heads"], s["dim"], s["ff"]
+        r, rd, qr = d // 4, 64, 3 * d // 8
+        scale = hd ** -0.5
+        for what, B, held, cnt in (("prompt", 1, 0, prompt), ("single tokens", batch, context, 1)):
+            M = B * cnt
+            pages = 64 * (-(-(held + cnt) // 64) + 1) * B
+            seen = lambda lo: sum(p - lo(p) + 1 for p in range(held, held + cnt)) * B      # (query, key) pairs
+            pairs_chunk = seen(lambda p: p - p % mask)
+            pairs_window = seen(lambda p: max(0, p + 1 - mask))
+            # ---- attention over keys and values of their own: the chunked mask beside the sliding window ----
+            for design, kw, pairs in (("forilorn", dict(chunk=mask), pairs_chunk), ("mosurax", dict(window=mask), pairs_window)):
+                need = KVNeed(G, hd, kw.get("window"), None, 0, kw.get("chunk"))
+                cache = SequenceCache([need], [None], pages, bf, dev, max_slots=B)
+                st = steps_for(cache, B, held, cnt)
+                group, layer = cache.kv_entry(0)
+                group.k_pool(layer).normal_(); group.v_pool(layer).normal_()
+                u = torch.randn((M, (2 * H + 2 * G) * hd), dtype=torch.float32, device=dev).to(bf)
+                o = torch.empty((M, H * hd), dtype=bf, device=dev)
+                us = timed(lambda: K.attention(u, group.k_pool(layer), group.v_pool(layer), group.page_table, st, o, H, G, hd, scale,
+                                               kw.get("window", 0), gate=u[:, (H + 2 * G) * hd:], chunk=kw.get("chunk", 0)))
+                keys = (pairs // cnt if cnt == 1 else min(held + cnt, 10 ** 9) * B)         # key rows read at least once
+                if cnt > 1 and "window" not in kw:
+                    keys = (held + cnt) * B
+                report(name, design, "attention, gated, " + ("chunked mask" if "chunk" in kw else "window"),
+                       f"{what}: {M} tokens, {B} seq of {held + cnt}, {H} heads over {G} of {hd}, mask {mask}", us,
+                       keys * G * 2 * hd * 2 + 3 * M * H * hd * 2, 4.0 * pairs * H * hd)
+                del cache
+            # ---- all heads over one cached row whose front is the value (the latent layer), a sliding window ----
+            cache = SequenceCache([KVNeed(1, r + rd, mask, 0)], [None], pages, bf, dev, max_slots=B)
+            st = steps_for(cache, B, held, cnt)
+            group, layer = cache.kv_entry(0)
+            group.k_pool(layer).normal_()
+            ql = torch.randn((M, H * (r + rd)), dtype=torch.float32, device=dev).to(bf)
+            gate = torch.randn((M, H), dtype=torch.float32, device=dev).to(bf)
+            o = torch.empty((M, H * r), dtype=bf, device=dev)
+            us = timed(lambda: K.attention(ql, group.k_pool(layer), group.k_pool(layer), group.page_table, st, o, H, 1, r + rd, scale, mask,
+                                           value_dim=r, gate=gate, gate_per_head=True, values_in_keys=True))
+            keys = pairs_window // cnt if cnt == 1 else (held + cnt) * B
+            report(name, "forilorn", "attention over one latent row, gate a head, window",
+                   f"{what}: {M} tokens, {B} seq of {held + cnt}, {H} heads over rows of {r} + {rd}, window {mask}", us,
+                   keys * (r + rd) * 2 + M * H * (2 * r + rd) * 2, 2.0 * pairs_window * H * (2 * r + rd))
+            del cache
+            # ---- what stands between the input product and the attention ----
+            cache = SequenceCache([KVNeed(G, hd, None, None, 0, mask), KVNeed(1, r + rd, mask, 0)], [None, None], 2 * pages, bf, dev, max_slots=B)
+            st = steps_for(cache, B, held, cnt)
+            (g0, l0), (g1, l1) = cache.kv_entry(0), cache.kv_entry(1)
+            inv = torch.rand(hd // 2, dtype=torch.float32, device=dev)
+            u = torch.randn((M, (2 * H + G) * hd), dtype=torch.float32, device=dev).to(bf)
+            us = timed(lambda: K.qk_rotate_unit(u, u, st.positions, st.slot_of_token, g0.page_table, inv, hd, True, 1e-6, H, G, hd,
+                                                g0.k_pool(l0), g0.v_pool(l0), value_from_key=True))
+            report(name, "forilorn", "rotation of pairs, unit heads, keys and values to pages", f"{what}: {M} tokens, {H} + {G} heads of {hd}", us,
+                   M * (2 * H + 3 * G) * hd * 2)
+            u3 = torch.randn((M, (H + 2 * G) * hd), dtype=torch.float32, device=dev).to(bf)
+            us = timed(lambda: K.rope_kv_write(u3, st.positions, st.slot_of_token, g0.page_table, inv, H, G, hd, hd, False,
+                                               g0.k_pool(l0), g0.v_pool(l0), value_dim=hd))
+            report(name, "mosurax", "rotation, keys and values to pages", f"{what}: {M} tokens, {H} + 2 x {G} heads of {hd}", us,
+                   M * (2 * H + 4 * G) * hd * 2)
+            ul = torch.randn((M, qr + r + rd + H), dtype=torch.float32, device=dev).to(bf)
+            cq = torch.empty((M, qr), dtype=bf, device=dev)
+            ones_q, ones_k = torch.ones(qr, dtype=torch.float32, device=dev), torch.ones(r, dtype=torch.float32, device=dev)
+            us = timed(lambda: K.latent_prepare(ul, qr, r, rd, ones_q, ones_k, 1e-6, cq, st.positions, st.slot_of_token, g1.page_table,
+                                                inv, rd, True, g1.k_pool(l1)))
+            report(name, "forilorn", "latents normed, rotary key turned, row to its page", f"{what}: {M} tokens, latents {qr} and {r} + {rd}", us,
+                   M * (2 * qr + 2 * (r + rd)) * 2)
+            qh = torch.randn((M, H * (hd + rd)), dtype=torch.float32, device=dev).to(bf)
+            qlat = torch.empty((M, H * (r + rd)), dtype=bf, device=dev)
+            us = timed(lambda: K.latent_query(qh, qlat, H, hd, rd, r, st.positions, inv, rd, True))
+            report(name, "forilorn", "query's rotary parts turned into place", f"{what}: {M} tokens, {H} heads of {hd} + {rd}", us, 2 * M * H * rd * 2)
+            del cache
+            # ---- the embedding with its pair table beside the plain one ----
+            V = s["vocab"]
+            table = torch.randn((V, d), dtype=torch.float32, device=dev).to(bf)
+            pair = torch.randn((65537, d), dtype=torch.float32, device=dev).to(bf)
+            ids = torch.randint(0, V, (M,), dtype=torch.int32, device=dev)
+            x = torch.empty((M, d), dtype=torch.float32, device=dev)
+            area = torch.zeros((B, 256), dtype=torch.uint8, device=dev)
+            err = torch.zeros(1, dtype=torch.int32, device=dev)
+            slots_tok, pos = i32([b for b in range(B) for _ in range(cnt)]), i32([held + t for _ in range(B) for t in range(cnt)])
+            cu = i32([cnt * b for b in range(B + 1)])
+            us = timed(lambda: K.embedding_pair(table, pair, ids, pos, slots_tok, cu, area[:, :4], 3.0, 31, 17, 65536, x, err))
+            report(name, "forilorn", "scaled embedding + hashed pair row", f"{what}: {M} tokens of {d}", us, M * d * (2 + 2 + 4))
+            us = timed(lambda: K.embedding(table, ids, x, err))
+            report(name, "mosurax", "embedding", f"{what}: {M} tokens of {d}", us, M * d * (2 + 4))
+            # ---- the feed-forward's first product with its activation in the epilogue ----
+            xn = torch.randn((M, d), dtype=torch.float32, device=dev).to(bf)
+            w1 = (torch.randn((ff, d), dtype=torch.float32, device=dev) * d ** -0.5).to(bf)
+            w2 = (torch.randn((2 * ff, d), dtype=torch.float32, device=dev) * d ** -0.5).to(bf)
+            h = torch.empty((M, ff), dtype=bf, device=dev)
+            us = timed(lambda: K.gemm_tc(xn, w1, h, K.OUT_GELU))
+            report(name, "forilorn", "up product, gelu in the epilogue", f"{what}: {M} x {d} -> {ff}", us, (w1.numel() + xn.numel() + h.numel()) * 2,
+                   2.0 * M * d * ff)
+            us = timed(lambda: K.gemm_tc(xn, w2, h, K.OUT_SWIGLU))
+            report(name, "mosurax", "gate and up product, silu * up in the epilogue", f"{what}: {M} x {d} -> 2 x {ff}", us,
+                   (w2.numel() + xn.numel() + h.numel()) * 2, 4.0 * M * d * ff)
+            # ---- a sublayer's normed output, scaled, into the stream ----
+            xs, y0 = torch.randn((M, d), dtype=torch.float32, device=dev), torch.randn((M, d), dtype=torch.float32, device=dev)
+            xb = torch.empty((M, d), dtype=bf, device=dev)
+            wd = torch.ones(d, dtype=torch.float32, device=dev)
+            us = timed(lambda: K.norm_add(xs, y0, 1.0, None, 0.0, wd, 1e-6, xb, out_scale=0.5))
+            report(name, "forilorn", "stream += m * norm(sublayer)", f"{what}: {M} x {d}", us, 3 * xs.numel() * 4 + xb.numel() * 2)
+    K.check_device_errors()
+    return lines
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--size", action="append", choices=sorted(SIZES), help="default: all")
-    ap.add_argument("--model", action="append", choices=["llama", "mosurax-dense", "mosurax-moe", "mogutar"], help="default: all four")
+    ap.add_argument("--model", action="append", choices=list(MODELS), help="default: all")
     ap.add_argument("--kernels", action="store_true", help="time the Mogutar design's own kernels alone instead")
+    ap.add_argument("--forilorn-kernels", action="store_true",
+                    help="time the Forilorn design's kernels alone, each beside the like kernel of the Mosurax design, instead")
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--batch", type=int, action="append", help="default: 8 and 64")
@@ -273,11 +458,14 @@ def main(argv=None) -> int:
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=8)
     a = ap.parse_args(argv)
+    if a.forilorn_kernels:
+        forilorn_kernel_times(a.size or sorted(SIZES), a.prompt, max(a.batch or (64,)), a.context, a.window or 1024)
+        return 0
     if a.kernels:
         kernel_times(a.size or sorted(SIZES), a.prompt, max(a.batch or (64,)))
         return 0
     run(a.size or sorted(SIZES), a.prompt, tuple(a.batch or (8, 64)), a.context, a.steps, a.warmup, a.window,
-        tuple(a.model or ("llama", "mosurax-dense", "mosurax-moe", "mogutar")))
+        tuple(a.model or MODELS))
     return 0
 
 

@@ -314,8 +314,12 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool, layer_index: int = 0)
         rows.append((f"{tag}_activation.silu_mul", timed(lambda: K.swiglu(gu, h, interleaved=ff.interleaved)), 3 * ff.I * esz))
         rows.append((f"{tag}_down", timed(lambda: linear(h, ff.wdown, x, OUT_ADD_F32, ff.bdown)), ff.wdown.numel() * ff.wdown.element_size()))
 
+    from .parts.mlp import DenseMLP
     if isinstance(ff, GatedMLP):
         dense_rows(ff, "ffn")
+    elif isinstance(ff, DenseMLP):        # no gate: the activation rides in the first product where the tensor cores run it
+        xf = xn.to(ff.wup.dtype)
+        rows.append(("ffn_up_gelu_down", timed(lambda: ff.forward(xf, x, None)), (ff.wup.numel() + ff.wdown.numel()) * ff.wup.element_size()))
     elif isinstance(ff, MoEMLP):          # router and the chosen experts of one token; the shared expert like a dense one
         xe = xn.to(ff.router.dtype)
         ids = torch.empty((1, ff.top), dtype=torch.int32, device=dev)
@@ -351,12 +355,13 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool, layer_index: int = 0)
         runner.cache.prepare([s], [1])
         q = torch.randn(1, max(qkv.shape[1], 8), device=dev).to(dt)
         o = torch.empty(1, att.H * att.vd, device=dev, dtype=dt)
-        n_qkv = (att.H + att.G) * att.hd + att.G * att.vd
+        n_qkv = (att.H + att.G) * att.hd + (0 if getattr(att, "value_from_key", False) else att.G * att.vd)
         gate = q[:, n_qkv:] if getattr(att, "gated", False) else None
         t = timed(lambda: K.attention(q, group.k_pool(layer), group.v_pool(layer), group.page_table, st, o, att.H, att.G, att.hd, att.scale,
                                       att.window or 0, value_dim=att.vd, sink=getattr(att, "sink", False), gate=gate,
-                                      softcap=getattr(att, "softcap", 0.0), keep_first=getattr(att, "keep_first", 0)))
-        seen = min(ctx + 1, att.window) if att.window else ctx + 1
+                                      softcap=getattr(att, "softcap", 0.0), keep_first=getattr(att, "keep_first", 0),
+                                      chunk=getattr(att, "chunk", None) or 0))
+        seen = min(ctx + 1, att.window) if att.window else ctx % att.chunk + 1 if getattr(att, "chunk", None) else ctx + 1
         rows.append((f"attn_scan.ctx{ctx}", t, seen * att.G * (att.hd + att.vd) * esz))
         eng.free_slot(s)
     if as_json:

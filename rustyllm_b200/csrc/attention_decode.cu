@@ -95,10 +95,19 @@ __device__ __forceinline__ float dec_peer_f32(const float* p, uint32_t rank) {
   return v;
 }
 
+// The first position that the query of a sequence of `len` tokens (itself at position len - 1) sees.  `window` carries
+// the layer's mask: W > 0, the last W positions; 0, all; -C < 0, a chunked mask: the positions of the query's own
+// block of C positions, blocks counted from the sequence's start.
+__device__ __forceinline__ int dec_start(int len, int window) {
+  if (window > 0) return len - window > 0 ? len - window : 0;
+  if (window < 0 && len > 0) return (len - 1) - (len - 1) % (-window);
+  return 0;
+}
+
 // ---- dealing chunks to sequences (warp-wide: call with all 32 lanes) ----
 // rounds of 64 keys (16 for each of the 4 warps) that sequence holds inside its window
 __device__ __forceinline__ int dec_rounds(int len, int window) {
-  const int start = (window > 0 && len - window > 0) ? len - window : 0;
+  const int start = dec_start(len, window);
   const int num_blk = (len + DEC_BLOCK - 1) / DEC_BLOCK - start / DEC_BLOCK;
   const int r = (num_blk + DEC_WARPS - 1) / DEC_WARPS;
   return r > 0 ? r : 1;
@@ -161,7 +170,7 @@ attention_decode_order_kernel(const int* __restrict__ seq_slots, const int* __re
   rl_pdl_wait();         // no early release of the kernels behind this one, as in the plan kernel
   const int b = threadIdx.x;
   int len = 0, inside = 0;
-  if (b < B) { len = kv_lens[b]; inside = (window > 0 && len > window) ? window : len; }
+  if (b < B) { len = kv_lens[b]; inside = len - dec_start(len, window); }
   s_len[b] = inside;
   __syncthreads();
   if (b < B) {
@@ -252,7 +261,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
   // a sequence that is one chunk (always so without splits; with a plan, the short ones beside
   // long ones) is finished here: no scratch, nothing for the combining kernel to do
   const bool direct = num_splits == 1;
-  const int start = (window > 0 && len - window > 0) ? len - window : 0;
+  const int start = dec_start(len, window);
   const int* pages = page_table + (size_t)cache_slot * max_pages;
 
   float acc[NT][4];
@@ -599,12 +608,12 @@ extern "C" long long rl_attention_decode_scratch_floats(int num_seqs, int num_he
 }
 
 // Deals num_seqs * num_splits chunks to the sequences by their lengths (inside `window`
-// if it is not 0).  plan: rl_attention_decode_plan_ints(...) ints, 16-byte aligned.  The
+// if it is positive; inside the query's block of -window positions if it is negative: a chunked mask).  plan: rl_attention_decode_plan_ints(...) ints, 16-byte aligned.  The
 // plan holds for every rl_attention_decode call with the same seq_slots, kv_lens, window
 // and num_splits: all layers of a step whose caches have the same window.
 extern "C" int rl_attention_decode_plan(const int* seq_slots, const int* kv_lens, int num_seqs, int window,
                                         int num_splits, int* plan, cudaStream_t stream) {
-  RL_REQUIRE(num_seqs >= 0 && num_splits >= 1 && window >= 0, "rl_attention_decode_plan: bad sizes");
+  RL_REQUIRE(num_seqs >= 0 && num_splits >= 1, "rl_attention_decode_plan: bad sizes");
   if (num_seqs == 0 || num_splits == 1) return RL_OK;
   RL_REQUIRE((long long)num_seqs * num_splits <= 65535, "rl_attention_decode_plan: %d sequences x %d splits exceed 65535 "
              "chunks; use fewer splits", num_seqs, num_splits);
@@ -649,8 +658,7 @@ extern "C" long long rl_attention_decode_order_ints(int num_seqs) { return 6LL *
 // rl_attention_decode call with the same seq_slots, kv_lens and window.
 extern "C" int rl_attention_decode_order(const int* seq_slots, const int* kv_lens, int num_seqs, int window, int* plan,
                                          cudaStream_t stream) {
-  RL_REQUIRE(num_seqs >= 0 && num_seqs <= 1024 && window >= 0, "rl_attention_decode_order: takes 0 to 1024 sequences (got %d) "
-             "and a window that is not negative", num_seqs);
+  RL_REQUIRE(num_seqs >= 0 && num_seqs <= 1024, "rl_attention_decode_order: takes 0 to 1024 sequences (got %d)", num_seqs);
   if (num_seqs == 0) return RL_OK;
   RL_REQUIRE(plan != nullptr && ((uintptr_t)plan & 15) == 0, "rl_attention_decode_order: plan is null or not 16-byte aligned");
   rl_launch_pdl(attention_decode_order_kernel, dim3(1), dim3((num_seqs + 31) / 32 * 32), 0, stream, seq_slots, kv_lens, num_seqs,
@@ -672,6 +680,7 @@ extern "C" int rl_attention_decode_order(const int* seq_slots, const int* kv_len
 // null): bf16 [num_seqs, ldg]; head h's output is multiplied element by element with
 // sigmoid(gate[b, h*head_dim + i]) before it is stored.  softcap > 0: a score s (scale included) becomes
 // softcap * tanh(s / softcap).  keep_first > 0 (with a window): positions [0, keep_first) stay visible.
+// window < 0: a chunked mask with blocks of -window positions (the query sees its own block up to itself).
 extern "C" int rl_attention_decode_masked(const void* q, int ldq, const void* k_pool, const void* v_pool,
                                           const int* page_table, int max_pages, const int* seq_slots, const int* kv_lens,
                                           void* out, int ldo, float* scratch, const int* plan, int num_seqs, int num_heads,
@@ -694,7 +703,6 @@ extern "C" int rl_attention_decode_masked(const void* q, int ldq, const void* k_
   RL_REQUIRE(num_splits == 1 || scratch != nullptr || (plan == nullptr && (num_splits == 2 || num_splits == 4 || num_splits == 8)),
              "rl_attention_decode: without scratch the chunks combine as a cluster, which takes 2, 4 or 8 splits and no plan (got %d)", num_splits);
   RL_REQUIRE(plan == nullptr || ((uintptr_t)plan & 15) == 0, "rl_attention_decode: plan is not 16-byte aligned");
-  RL_REQUIRE(window >= 0, "rl_attention_decode: negative window");
   if (num_seqs == 0) return RL_OK;
   const size_t parts = (size_t)num_seqs * num_heads * num_splits;
   float* part_o = scratch;

@@ -196,7 +196,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ kv_lens, int num_seqs, __nv_bfloat16* __restrict__ out, int ldo,
                             int H, int G, float scale_log2e, int window, int* __restrict__ err,
                             const int* __restrict__ tile_order, int sink, const __nv_bfloat16* __restrict__ gate, int ldg,
-                            float cap_in, float cap_out, int keep_first) {
+                            float cap_in, float cap_out, int keep_first, int chunk) {
   extern __shared__ uint8_t fa_smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)fa_smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* q_tile = smem;                                   // [2 halves][128 x 64]
@@ -284,7 +284,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     rows_here = min(TQ, q_len - qt0);
     pages = page_table + (size_t)seq_slots[b] * max_pages;
     const int last_pos = start_pos + qt0 + rows_here - 1;
-    const int first_key = window > 0 ? max(0, start_pos + qt0 + 1 - window) : 0;
+    // the first key that the tile's first row sees: the start of its window, or of its block of `chunk` positions
+    const int first_key = chunk > 0 ? (start_pos + qt0) / chunk * chunk : window > 0 ? max(0, start_pos + qt0 + 1 - window) : 0;
     kt_begin = first_key / TK; kt_end = last_pos / TK + 1;
     // kept first tokens: the key tiles that hold positions [0, keep_first) and lie wholly in front of the
     // window's first tile are walked first (place i of the walk is tile i there, kt_begin + i - kept_tiles behind)
@@ -399,6 +400,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int quarter = warp & 3, grp = (warp - 4) >> 2;
       const int r = quarter * 32 + lane;                      // row of the tile = lane of tensor memory
       const int pos = start_pos + qt0 + r;                    // position of this row's query
+      const int lo = chunk > 0 ? pos - pos % chunk : pos + 1 - window;   // the first position it sees (kept first tokens aside)
       const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
       float m_mine = -INFINITY, l_run = 0.f;                  // maximum this group's sum is scaled by; the sum
       bool ok = true;                                         // warp-uniform
@@ -430,15 +432,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         // The tile on the diagonal (no window) has code of its own, by 32-key chunks; every other tile
         // runs straight-line code over all 128 scores, which the scheduler can reorder freely.
-        const bool diag = window <= 0 && key0 + TK - 1 > start_pos + qt0;     // warp-uniform
+        const bool diag = window <= 0 && chunk <= 0 && key0 + TK - 1 > start_pos + qt0;     // warp-uniform
         int live = TK / 32;                     // diagonal tile: chunks that some row of this warp sees
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
         if (!diag) {
-          if (window > 0) {
+          if (window > 0 || chunk > 0) {
 #pragma unroll
             for (int j = 0; j < TK; ++j) {
               const int key = key0 + j;
-              if (!(key <= pos && (key > pos - window || key < keep_first))) sa[j] = 0xff800000u;          // -inf
+              if (!(key <= pos && (key >= lo || key < keep_first))) sa[j] = 0xff800000u;          // -inf
             }
           }
 #pragma unroll
@@ -654,13 +656,16 @@ extern "C" int rl_attention_prefill_tc_supported(int num_heads, int num_kv_heads
 // sink != 0: one more term of score 0 in the softmax's denominator.  gate (may be null): bf16 [M, ldg],
 // 16-byte aligned with ldg a multiple of 8; the output is multiplied by sigmoid(gate[m, h*head_dim + i]).
 // softcap > 0: a score s (scale included) becomes softcap * tanh(s / softcap).  keep_first > 0 (with a window):
-// positions [0, keep_first) stay visible behind the window.
-extern "C" int rl_attention_prefill_tc_masked(const void* q, int ldq, const void* k_pool, const void* v_pool, int num_pages,
+// positions [0, keep_first) stay visible behind the window.  chunk > 0 (instead of a window): a query at position p sees
+// positions [p - p % chunk, p], the positions of its own block counted from the sequence's start.
+extern "C" int rl_attention_prefill_tc_shaped(const void* q, int ldq, const void* k_pool, const void* v_pool, int num_pages,
                                               const int* page_table, int max_pages, const int* cu_seqlens,
                                               const int* seq_slots, const int* kv_lens, int num_seqs, int num_tiles,
                                               int num_tokens, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
                                               float scale, int window, int* err, const int* tile_order, int sink,
-                                              const void* gate, int ldg, float softcap, int keep_first, cudaStream_t stream) {
+                                              const void* gate, int ldg, float softcap, int keep_first, int chunk,
+                                              cudaStream_t stream) {
+  RL_REQUIRE(chunk >= 0 && !(chunk > 0 && window > 0), "rl_attention_prefill_tc: a chunked mask and a window exclude one another");
   RL_REQUIRE(softcap >= 0.f && keep_first >= 0 && scale > 0.f, "rl_attention_prefill_tc: negative soft cap or number of kept first tokens, or a scale that is not positive");
   const float cap_in = softcap > 0.f ? scale / softcap : 0.f, cap_out = softcap > 0.f ? softcap / scale : 0.f;
   if (window <= 0) keep_first = 0;
@@ -696,16 +701,27 @@ extern "C" int rl_attention_prefill_tc_masked(const void* q, int ldq, const void
       ? rl_launch_pdl(attention_prefill_tc_kernel<128>, dim3(num_heads, num_tiles), dim3(FA_THREADS), (size_t)FaSizes<128>::SMEM, stream,
                       mq, mk, mv, page_table, max_pages, cu_seqlens, seq_slots, kv_lens, num_seqs,
                       (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err, tile_order,
-                      sink, (const __nv_bfloat16*)gate, ldg, cap_in, cap_out, keep_first)
+                      sink, (const __nv_bfloat16*)gate, ldg, cap_in, cap_out, keep_first, chunk)
       : rl_launch_pdl(attention_prefill_tc_kernel<64>, dim3(num_heads, num_tiles), dim3(FA_THREADS), (size_t)FaSizes<64>::SMEM, stream,
                       mq, mk, mv, page_table, max_pages, cu_seqlens, seq_slots, kv_lens, num_seqs,
                       (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err, tile_order,
-                      sink, (const __nv_bfloat16*)gate, ldg, cap_in, cap_out, keep_first);
+                      sink, (const __nv_bfloat16*)gate, ldg, cap_in, cap_out, keep_first, chunk);
   if (e != cudaSuccess) {
     rl_set_error("rl_attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
     return RL_ERR_CUDA;
   }
   return RL_OK;
+}
+
+extern "C" int rl_attention_prefill_tc_masked(const void* q, int ldq, const void* k_pool, const void* v_pool, int num_pages,
+                                              const int* page_table, int max_pages, const int* cu_seqlens,
+                                              const int* seq_slots, const int* kv_lens, int num_seqs, int num_tiles,
+                                              int num_tokens, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
+                                              float scale, int window, int* err, const int* tile_order, int sink,
+                                              const void* gate, int ldg, float softcap, int keep_first, cudaStream_t stream) {
+  return rl_attention_prefill_tc_shaped(q, ldq, k_pool, v_pool, num_pages, page_table, max_pages, cu_seqlens, seq_slots, kv_lens,
+                                        num_seqs, num_tiles, num_tokens, out, ldo, num_heads, num_kv_heads, head_dim, scale, window,
+                                        err, tile_order, sink, gate, ldg, softcap, keep_first, 0, stream);
 }
 
 extern "C" int rl_attention_prefill_tc_gated(const void* q, int ldq, const void* k_pool, const void* v_pool, int num_pages,

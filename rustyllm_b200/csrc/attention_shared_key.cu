@@ -1,0 +1,312 @@
+// Attention of many query heads over ONE cached row a position whose front part is also the value
+// (attention through a latent: the row is [latent | rotary key part], the value is the latent), on
+// the tensor cores, for prompt portions and single tokens alike.
+//
+//   s_ij = (q_i . row_j) * scale over all DK elements,  j <= i,  i - j < window (if window > 0)
+//   o_i  = sigmoid(gate_i) * sum_j softmax_j(s_ij) row_j[0 .. DV)        (gate: one number a token and head)
+//
+// The rows of a tile are (token, head) pairs of one sequence: HG = min(H, 16) heads of TOK = 16 / HG
+// consecutive tokens (more than 16 heads: groups of 16 along grid y).  All of them read the same keys,
+// so a block of 64 keys (one page) is brought into shared memory once a tile and serves both products:
+//   1. warp w: S[16 x 16] = Q[16 x DK] . K[16w .. 16w + 16)^T   (mma.sync m16n8k16, Q and K by ldmatrix)
+//      scaled into the exp2 domain, masked, to shared memory
+//   2. warp w: rows 4w .. 4w + 3: running maximum and sum, P = exp2(S - max) as bf16 to shared memory
+//   3. warp w: O[16 x its quarter of DV] = O * corr + P[16 x 64] . K[64 x its columns]  (values by
+//      ldmatrix.trans from the same key block)
+// Key blocks are double-buffered with cp.async.  What a row sums, and in which order, depends on its
+// position, the window and the page borders alone - not on the batch or on how a prompt was cut.
+#include <math.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+#define SK_WARPS 4
+#define SK_ROWS 16
+#define SK_KEYS RL_PAGE      // keys a block: one page
+
+__device__ __forceinline__ void sk_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void sk_cp16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void sk_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void sk_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void sk_ldm4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void sk_ldm4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// Shared memory: the query tile [16][DK + 8] bf16, two key blocks [64][DK + 8] bf16 (8 elements of padding
+// make a row an odd number of 16-byte pieces: ldmatrix without bank conflicts), the scores [16][64 + 4]
+// float, the weights [16][64 + 8] bf16, and a row's correction factor [16].
+struct SkLayout {
+  int ldk;              // elements from row to row of the query tile and the key blocks
+  uint32_t q_off, k_off, s_off, p_off, c_off, bytes;
+};
+__host__ __device__ inline SkLayout sk_layout(int DK) {
+  SkLayout L;
+  L.ldk = DK + 8;
+  L.q_off = 0;
+  L.k_off = L.q_off + SK_ROWS * L.ldk * 2;
+  L.s_off = L.k_off + 2 * SK_KEYS * L.ldk * 2;
+  L.p_off = L.s_off + SK_ROWS * (SK_KEYS + 4) * 4;
+  L.c_off = L.p_off + SK_ROWS * (SK_KEYS + 8) * 2;
+  L.bytes = L.c_off + SK_ROWS * 4;
+  return L;
+}
+
+// NTW: output n-tiles (8 columns each) a warp owns; 4 * NTW * 8 >= DV.
+template <int NTW>
+__global__ void __launch_bounds__(SK_WARPS * 32)
+attention_shared_key_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ k_pool,
+                            const int* __restrict__ page_table, int max_pages, const int* __restrict__ cu_seqlens,
+                            const int* __restrict__ seq_slots, const int* __restrict__ kv_lens, int num_seqs,
+                            int one_token_each, __nv_bfloat16* __restrict__ out, int ldo,
+                            const __nv_bfloat16* __restrict__ gate, int ldg, int H, int DK, int DV, float scale_log2e,
+                            int window) {
+  extern __shared__ __align__(128) uint8_t sk_smem[];
+  __shared__ int s_where[2];
+  const SkLayout L = sk_layout(DK);
+  const int ldk = L.ldk;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int HG = H < 16 ? H : 16;              // heads a tile
+  const int TOK = SK_ROWS / HG;                // tokens a tile
+  // ---- which sequence, which tile of its tokens ----
+  if (one_token_each) {
+    if (threadIdx.x == 0) { s_where[0] = blockIdx.x; s_where[1] = 0; }
+  } else if (threadIdx.x == 0) {
+    int x = blockIdx.x, b = 0;
+    for (; b < num_seqs; ++b) {
+      const int n = (cu_seqlens[b + 1] - cu_seqlens[b] + TOK - 1) / TOK;
+      if (x < n) break;
+      x -= n;
+    }
+    s_where[0] = b; s_where[1] = x;
+  }
+  __syncthreads();
+  const int b = s_where[0];
+  if (b >= num_seqs) return;                   // the grid is sized exactly; defensive
+  const int row0 = cu_seqlens[b], q_len = cu_seqlens[b + 1] - row0, kv_len = kv_lens[b];
+  const int start_pos = kv_len - q_len;
+  const int tok0 = s_where[1] * TOK;
+  const int toks_here = min(TOK, q_len - tok0);
+  const int head0 = blockIdx.y * 16;
+  const int* pages = page_table + (size_t)seq_slots[b] * max_pages;
+  const uint32_t smem = (uint32_t)__cvta_generic_to_shared(sk_smem);
+  float* s_s = reinterpret_cast<float*>(sk_smem + L.s_off);
+  __nv_bfloat16* s_p = reinterpret_cast<__nv_bfloat16*>(sk_smem + L.p_off);
+  float* s_c = reinterpret_cast<float*>(sk_smem + L.c_off);
+
+  const int pos_first = start_pos + tok0, pos_last = pos_first + toks_here - 1;
+  const int first_key = window > 0 ? max(0, pos_first + 1 - window) : 0;
+  const int kb_begin = first_key / SK_KEYS, kb_end = pos_last / SK_KEYS + 1;
+  const int pieces_row = DK >> 3;              // 16-byte pieces a row
+
+  // ---- the query tile: row r = (token r / HG, head head0 + r % HG); rows without a token or head are zero ----
+  for (int i = threadIdx.x; i < SK_ROWS * pieces_row; i += SK_WARPS * 32) {
+    const int r = i / pieces_row, ch = i % pieces_row;
+    const int tok = r / HG, head = head0 + r % HG;
+    const uint32_t dst = smem + L.q_off + (uint32_t)(r * ldk * 2 + ch * 16);
+    if (tok < toks_here && head < H) sk_cp16(dst, q + (size_t)(row0 + tok0 + tok) * ldq + (size_t)head * DK + ch * 8);
+    else *reinterpret_cast<uint4*>(sk_smem + L.q_off + r * ldk * 2 + ch * 16) = make_uint4(0u, 0u, 0u, 0u);
+  }
+  auto issue = [&](int kb, int buf) {
+    const __nv_bfloat16* src = k_pool + (size_t)pages[kb] * SK_KEYS * DK;
+    const uint32_t dst = smem + L.k_off + (uint32_t)(buf * SK_KEYS * ldk * 2);
+    for (int i = threadIdx.x; i < SK_KEYS * pieces_row; i += SK_WARPS * 32) {
+      const int row = i / pieces_row, ch = i % pieces_row;
+      sk_cp16(dst + (uint32_t)(row * ldk * 2 + ch * 16), src + (size_t)i * 8);
+    }
+  };
+  issue(kb_begin, 0);
+  sk_commit();
+
+  float acc[NTW][4];
+#pragma unroll
+  for (int j = 0; j < NTW; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  // softmax state of row 4 * warp + lane / 8 (the same in its 8 lanes)
+  float m_run = -INFINITY, l_run = 0.f;
+  const int r8 = lane & 7, mat = lane >> 3;
+  // this lane's two rows of the score and output fragments
+  const int tok_lo = g / HG, tok_hi = (g + 8) / HG;
+  const bool valid_lo = tok_lo < toks_here && head0 + g % HG < H, valid_hi = tok_hi < toks_here && head0 + (g + 8) % HG < H;
+  const int pos_lo = pos_first + tok_lo, pos_hi = pos_first + tok_hi;
+  const int nt_total = DV >> 3;
+
+  for (int kb = kb_begin; kb < kb_end; ++kb) {
+    const int buf = (kb - kb_begin) & 1;
+    sk_wait<0>();
+    __syncthreads();                           // block kb (and the queries) have landed; everyone is done with block kb - 1
+    if (kb + 1 < kb_end) { issue(kb + 1, buf ^ 1); sk_commit(); }
+    const uint32_t kbase = smem + L.k_off + (uint32_t)(buf * SK_KEYS * ldk * 2);
+    // ---- 1. scores of this warp's 16 keys ----
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    {
+      const uint32_t qa = smem + L.q_off + (uint32_t)(((r8 + 8 * (mat & 1)) * ldk + 8 * (mat >> 1)) * 2);
+      const uint32_t ka = kbase + (uint32_t)(((16 * warp + r8 + 8 * (mat >> 1)) * ldk + 8 * (mat & 1)) * 2);
+      for (int ks = 0; ks < DK; ks += 16) {
+        uint32_t a[4], bb[4];
+        sk_ldm4(a, qa + ks * 2);
+        sk_ldm4(bb, ka + ks * 2);
+        sk_mma(s[0], a[0], a[1], a[2], a[3], bb[0], bb[1]);
+        sk_mma(s[1], a[0], a[1], a[2], a[3], bb[2], bb[3]);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const int col = 16 * warp + 8 * nt + 2 * t;
+      const int key = kb * SK_KEYS + col;
+      float v[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int k = key + (e & 1), pos = e < 2 ? pos_lo : pos_hi;
+        const bool ok = (e < 2 ? valid_lo : valid_hi) && k <= pos && (window <= 0 || k > pos - window);
+        v[e] = ok ? s[nt][e] * scale_log2e : -INFINITY;
+      }
+      *reinterpret_cast<float2*>(&s_s[g * (SK_KEYS + 4) + col]) = make_float2(v[0], v[1]);
+      *reinterpret_cast<float2*>(&s_s[(g + 8) * (SK_KEYS + 4) + col]) = make_float2(v[2], v[3]);
+    }
+    __syncthreads();
+    // ---- 2. rows 4 * warp .. + 3: eight lanes a row, eight scores a lane ----
+    {
+      const int row = 4 * warp + (lane >> 3), sub = lane & 7;
+      const float4 x0 = *reinterpret_cast<const float4*>(&s_s[row * (SK_KEYS + 4) + 8 * sub]);
+      const float4 x1 = *reinterpret_cast<const float4*>(&s_s[row * (SK_KEYS + 4) + 8 * sub + 4]);
+      float mx = fmaxf(fmaxf(fmaxf(x0.x, x0.y), fmaxf(x0.z, x0.w)), fmaxf(fmaxf(x1.x, x1.y), fmaxf(x1.z, x1.w)));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      const float m_new = fmaxf(m_run, mx);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;        // a row that has seen nothing yet
+      const float corr = exp2f(m_run - m_use);
+      const float p0 = exp2f(x0.x - m_use), p1 = exp2f(x0.y - m_use), p2 = exp2f(x0.z - m_use), p3 = exp2f(x0.w - m_use);
+      const float p4 = exp2f(x1.x - m_use), p5 = exp2f(x1.y - m_use), p6 = exp2f(x1.z - m_use), p7 = exp2f(x1.w - m_use);
+      float sum = ((p0 + p1) + (p2 + p3)) + ((p4 + p5) + (p6 + p7));
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      l_run = l_run * corr + sum;
+      m_run = m_new;
+      __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(p4, p5), h3 = __floats2bfloat162_rn(p6, p7);
+      uint4 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+      pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+      *reinterpret_cast<uint4*>(&s_p[row * (SK_KEYS + 8) + 8 * sub]) = pk;
+      if (sub == 0) s_c[row] = corr;
+    }
+    __syncthreads();
+    // ---- 3. this warp's columns of the output ----
+    {
+      const float c_lo = s_c[g], c_hi = s_c[g + 8];
+#pragma unroll
+      for (int j = 0; j < NTW; ++j) { acc[j][0] *= c_lo; acc[j][1] *= c_lo; acc[j][2] *= c_hi; acc[j][3] *= c_hi; }
+      const uint32_t pa = smem + L.p_off + (uint32_t)(((r8 + 8 * (mat & 1)) * (SK_KEYS + 8) + 8 * (mat >> 1)) * 2);
+#pragma unroll
+      for (int kk = 0; kk < SK_KEYS / 16; ++kk) {
+        uint32_t a[4];
+        sk_ldm4(a, pa + kk * 32);
+        const uint32_t va = kbase + (uint32_t)(((16 * kk + r8 + 8 * (mat & 1)) * ldk + 8 * (mat >> 1)) * 2);
+#pragma unroll
+        for (int jp = 0; jp < NTW / 2; ++jp) {
+          const int nt = warp * NTW + 2 * jp;
+          if (nt < nt_total) {                 // warp-uniform
+            uint32_t bb[4];
+            sk_ldm4_trans(bb, va + nt * 16);
+            sk_mma(acc[2 * jp], a[0], a[1], a[2], a[3], bb[0], bb[1]);
+            sk_mma(acc[2 * jp + 1], a[0], a[1], a[2], a[3], bb[2], bb[3]);
+          }
+        }
+      }
+    }
+  }
+  // ---- the rows' sums to everyone; normalise, gate, store ----
+  __syncthreads();
+  if ((lane & 7) == 0) s_c[4 * warp + (lane >> 3)] = l_run;
+  __syncthreads();
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = g + 8 * half;
+    if (!(half ? valid_hi : valid_lo)) continue;
+    const int tok = r / HG, head = head0 + r % HG;
+    const size_t m = (size_t)(row0 + tok0 + tok);
+    const float l = s_c[r];
+    float f = l > 0.f ? 1.0f / l : 0.f;
+    if (gate) f *= 1.0f / (1.0f + expf(-__bfloat162float(gate[m * ldg + head])));
+    __nv_bfloat16* orow = out + m * ldo + (size_t)head * DV;
+#pragma unroll
+    for (int j = 0; j < NTW; ++j) {
+      const int nt = warp * NTW + j;
+      if (nt < nt_total)
+        *reinterpret_cast<__nv_bfloat162*>(orow + 8 * nt + 2 * t) = __floats2bfloat162_rn(acc[j][2 * half] * f, acc[j][2 * half + 1] * f);
+    }
+  }
+}
+
+// 1 if the kernel takes this shape: rows of key_dim elements (a multiple of 16) whose first value_dim (a multiple of
+// 8, at most 512) are the value, and a key block pair that fits shared memory.
+extern "C" int rl_attention_shared_key_supported(int num_heads, int key_dim, int value_dim) {
+  if (num_heads <= 0 || key_dim <= 0 || key_dim % 16 != 0 || value_dim <= 0 || value_dim % 8 != 0) return 0;
+  if (value_dim > key_dim || value_dim > 512) return 0;
+  return sk_layout(key_dim).bytes <= 227u * 1024u ? 1 : 0;
+}
+
+// q: [M, ldq] bf16, head h at columns [h * key_dim, (h + 1) * key_dim), the step's tokens packed by sequence
+// (cu_seqlens: [B + 1] offsets; kv_lens[b]: the sequence's length after this step).  k_pool: [pages, 1, RL_PAGE,
+// key_dim] bf16.  out: [M, ldo] bf16, head h at columns [h * value_dim, ...).  gate (may be null): bf16 [M, ldg], one
+// number a head.  tokens_per_tile = 16 / min(num_heads, 16); num_tiles = sum over sequences of
+// ceil(tokens / tokens_per_tile).  one_token_each != 0: every sequence brings one token (num_tiles = num_seqs).
+// window > 0: a query at position i sees positions j with 0 <= i - j < window; 0: all j <= i.
+extern "C" int rl_attention_shared_key(const void* q, int ldq, const void* k_pool, const int* page_table, int max_pages,
+                                       const int* cu_seqlens, const int* seq_slots, const int* kv_lens, int num_seqs,
+                                       int num_tiles, int one_token_each, void* out, int ldo, const void* gate, int ldg,
+                                       int num_heads, int key_dim, int value_dim, float scale, int window,
+                                       cudaStream_t stream) {
+  RL_REQUIRE(rl_attention_shared_key_supported(num_heads, key_dim, value_dim),
+             "rl_attention_shared_key: unsupported shape (heads %d, key rows of %d, values of %d): key rows must be a multiple "
+             "of 16, values a multiple of 8 and at most 512", num_heads, key_dim, value_dim);
+  RL_REQUIRE(num_seqs >= 0 && num_tiles >= 0 && window >= 0, "rl_attention_shared_key: bad sizes");
+  RL_REQUIRE(ldq >= num_heads * key_dim && ldq % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)k_pool & 15) == 0,
+             "rl_attention_shared_key: q and the pool must be 16-byte aligned, q's row stride a multiple of 8 that holds all heads");
+  RL_REQUIRE(ldo >= num_heads * value_dim && ldo % 2 == 0 && ((uintptr_t)out & 3) == 0,
+             "rl_attention_shared_key: the output's row stride is too small or odd, or the output is misaligned");
+  RL_REQUIRE(gate == nullptr || ldg >= num_heads, "rl_attention_shared_key: the gate's row stride is too small");
+  RL_REQUIRE(!one_token_each || num_tiles == num_seqs, "rl_attention_shared_key: one token a sequence means a tile a sequence");
+  if (num_seqs == 0 || num_tiles == 0) return RL_OK;
+  const int groups = (num_heads + 15) / 16;
+  RL_REQUIRE(groups <= 65535, "rl_attention_shared_key: too many heads");
+  const SkLayout L = sk_layout(key_dim);
+  const dim3 grid(num_tiles, groups), block(SK_WARPS * 32);
+  const float sl2 = scale * 1.4426950408889634f;
+#define RL_SK_LAUNCH(NTW)                                                                                                   \
+  do {                                                                                                                      \
+    static int reserved = 0;                                                                                                \
+    if ((int)L.bytes > reserved) {                                                                                          \
+      cudaError_t e = cudaFuncSetAttribute(attention_shared_key_kernel<NTW>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                           (int)L.bytes);                                                                   \
+      RL_REQUIRE(e == cudaSuccess, "rl_attention_shared_key: cannot reserve %u bytes of shared memory: %s", L.bytes,        \
+                 cudaGetErrorString(e));                                                                                    \
+      reserved = (int)L.bytes;                                                                                              \
+    }                                                                                                                       \
+    attention_shared_key_kernel<NTW><<<grid, block, L.bytes, stream>>>(                                                     \
+        (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, page_table, max_pages, cu_seqlens, seq_slots, kv_lens,  \
+        num_seqs, one_token_each, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)gate, ldg, num_heads, key_dim, value_dim, \
+        sl2, window);                                                                                                       \
+  } while (0)
+  if (value_dim <= 64) RL_SK_LAUNCH(2);
+  else if (value_dim <= 128) RL_SK_LAUNCH(4);
+  else if (value_dim <= 256) RL_SK_LAUNCH(8);
+  else RL_SK_LAUNCH(16);
+#undef RL_SK_LAUNCH
+  RL_LAUNCH_CHECK("rl_attention_shared_key");
+  return RL_OK;
+}

@@ -1,5 +1,5 @@
 // Attention of the step's query tokens over the paged key/value cache, on the CUDA
-// cores, for any head size up to 256 (steps of 2), any number of heads and groups,
+// cores, for any head size up to 1,024 (steps of 2), any number of heads and groups,
 // float or bf16 storage.  Serves prefill and decode alike: a query token at
 // position p attends to cached positions [max(0, p + 1 - window), p] of its own
 // sequence (with `chunk` > 0 instead: to [p - p % chunk, p], the positions of its own
@@ -24,9 +24,9 @@
 #include "common.cuh"
 
 #define ATT_WARPS 8
-#define ATT_MAX_HD 256
+#define ATT_MAX_HD 1024        // rows of 256 elements and less run the kernel with 8 elements a lane, wider ones with 32
 
-template <typename T>
+template <typename T, int NE>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_pool,
                       const T* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
@@ -34,8 +34,7 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
                       T* __restrict__ out, int ldo, int H, int G, int hd, int vd, float scale, int window,
                       int sink, const T* __restrict__ gate, int ldg, float softcap, int keep_first, int chunk, int ldv,
                       int gate_per_head) {
-  constexpr int NE = ATT_MAX_HD / 32;
-  __shared__ float s_acc[ATT_WARPS][ATT_MAX_HD];
+  __shared__ float s_acc[ATT_WARPS][NE * 32];
   __shared__ float s_max[ATT_WARPS], s_sum[ATT_WARPS];
   const int m = blockIdx.x, h = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -169,18 +168,20 @@ extern "C" int rl_attention_simt_shaped(const void* q, int ldq, const void* k_po
   RL_REQUIRE(window >= 0, "rl_attention_simt: negative window");
   if (num_tokens == 0) return RL_OK;
   dim3 grid(num_tokens, num_heads);
-  if (dtype == RL_F32)
-    attention_simt_kernel<float><<<grid, ATT_WARPS * 32, 0, stream>>>(
-        (const float*)q, ldq, (const float*)k_pool, (const float*)v_pool, page_table, max_pages,
-        slot_of_token, positions, (float*)out, ldo, num_heads, num_kv_heads, head_dim, value_dim, scale, window,
-        sink, (const float*)gate, ldg, softcap, keep_first, chunk, ldv, gate_per_head);
-  else if (dtype == RL_BF16)
-    attention_simt_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, 0, stream>>>(
-        (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table,
-        max_pages, slot_of_token, positions, (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, head_dim, value_dim, scale, window,
-        sink, (const __nv_bfloat16*)gate, ldg, softcap, keep_first, chunk, ldv, gate_per_head);
-  else
+  const bool wide = head_dim > 256 || value_dim > 256;
+#define RL_ATT_SIMT_LAUNCH(T, NE)                                                                                         \
+  attention_simt_kernel<T, NE><<<grid, ATT_WARPS * 32, 0, stream>>>(                                                      \
+      (const T*)q, ldq, (const T*)k_pool, (const T*)v_pool, page_table, max_pages, slot_of_token, positions, (T*)out, ldo, \
+      num_heads, num_kv_heads, head_dim, value_dim, scale, window, sink, (const T*)gate, ldg, softcap, keep_first, chunk,  \
+      ldv, gate_per_head)
+  if (dtype == RL_F32) {
+    if (wide) RL_ATT_SIMT_LAUNCH(float, 32); else RL_ATT_SIMT_LAUNCH(float, 8);
+  } else if (dtype == RL_BF16) {
+    if (wide) RL_ATT_SIMT_LAUNCH(__nv_bfloat16, 32); else RL_ATT_SIMT_LAUNCH(__nv_bfloat16, 8);
+  } else {
     RL_REQUIRE(false, "rl_attention_simt: unknown dtype %d", dtype);
+  }
+#undef RL_ATT_SIMT_LAUNCH
   RL_LAUNCH_CHECK("rl_attention_simt");
   return RL_OK;
 }

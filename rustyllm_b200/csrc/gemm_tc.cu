@@ -167,7 +167,8 @@ __device__ __forceinline__ void tile_epilogue(uint32_t tmem_acc, int quarter, in
         if (m < M) {
           const float v = __uint_as_float(r[j]) + b;
           const size_t o = (size_t)m * ldo + n;
-          if (out_mode == TC_OUT_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
+          if (out_mode == TC_OUT_GELU) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(gelu_tanh_f(v));
+          else if (out_mode == TC_OUT_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v);
           else ((float*)out)[o] = v;
         }
       }
@@ -786,7 +787,7 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
   const float* norm_weight = fuse.norm_weight;
   RL_REQUIRE(rl_gemm_tc_supported(A, W, M, N, K, lda), "rl_gemm_tc: operands not supported (M=%d N=%d K=%d lda=%d; K and lda "
              "must be multiples of 8 and the bases 16-byte aligned)", M, N, K, lda);
-  RL_REQUIRE(out_mode >= 0 && out_mode <= 4, "rl_gemm_tc: unknown output mode %d", out_mode);
+  RL_REQUIRE(out_mode >= 0 && out_mode <= 5, "rl_gemm_tc: unknown output mode %d", out_mode);
   RL_REQUIRE(out_mode != TC_OUT_SWIGLU || N % 2 == 0, "rl_gemm_tc: the SwiGLU epilogue needs an even number of weight rows, got %d", N);
   RL_REQUIRE(ldo >= (out_mode == TC_OUT_SWIGLU ? N / 2 : N) && err != nullptr, "rl_gemm_tc: bad output stride or null error word");
   RL_REQUIRE(force_splits >= 0 && force_splits <= 8, "rl_gemm_tc: the number of K parts must be 1 to 8 (0: chosen from the shapes), got %d", force_splits);

@@ -7,10 +7,16 @@
 
 #include "common.cuh"
 
-enum { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_ADD_F32 = 2, TC_OUT_SWIGLU = 3, TC_OUT_ROPE_KV = 4 };
+// TC_OUT_GELU: as TC_OUT_BF16, the stored value being the tanh form of gelu of the product (plus bias)
+enum { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_ADD_F32 = 2, TC_OUT_SWIGLU = 3, TC_OUT_ROPE_KV = 4, TC_OUT_GELU = 5 };
 
 // silu(g) * u for a result that is stored in bf16: the fast exponential and division are
 // accurate to a few units in the last place of a float, far below bf16's rounding step
+// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) = z / (1 + e^{-2y}), y the tanh's argument
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  const float y = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+  return z * __fdividef(1.0f, 1.0f + __expf(-2.0f * y));
+}
 __device__ __forceinline__ float silu_mul(float g, float u) { return g * __fdividef(1.0f, 1.0f + __expf(-g)) * u; }
 
 // The optional norm work of an epilogue.
@@ -276,6 +282,10 @@ __device__ __forceinline__ void tc_finish_column(float4 v, int j, int r4, int la
           break;
         }
         const size_t o = (size_t)(m0 + j) * ldo + nn;
+        if (out_mode == TC_OUT_GELU) {
+          v = make_float4(gelu_tanh_f(v.x), gelu_tanh_f(v.y), gelu_tanh_f(v.z), gelu_tanh_f(v.w));
+          out_mode = TC_OUT_BF16;
+        }
         if (vec_ok) {
           if (out_mode == TC_OUT_BF16) {
             __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);

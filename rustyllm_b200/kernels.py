@@ -17,6 +17,7 @@ from .csrc import build as _build
 
 F32, BF16 = 0, 1
 OUT_SAME, OUT_F32, OUT_ADD_F32, OUT_SWIGLU = 0, 1, 2, 3
+OUT_GELU = 5        # the tensor-core product alone: bf16 out = gelu_tanh(product)
 
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
@@ -53,6 +54,9 @@ _SIGNATURES = {
     "rl_attention_simt_shaped": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
                                  _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                                  _c_int, _c_void_p, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "rl_attention_shared_key_supported": [_c_int, _c_int, _c_int],
+    "rl_attention_shared_key": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                                _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p],
     "rl_embedding_pair": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll,
                           _c_float, _c_ll, _c_ll, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_gelu_tanh": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
@@ -116,6 +120,9 @@ _SIGNATURES = {
     "rl_attention_prefill_tc_masked": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                                        _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
                                        _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_float, _c_int, _c_void_p],
+    "rl_attention_prefill_tc_shaped": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                                       _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                       _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_float, _c_int, _c_int, _c_void_p],
     "rl_attention_decode_plan": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_attention_decode_order": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_attention_decode_places": [_c_int],
@@ -898,7 +905,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int,
             norm_sumsq: Optional[torch.Tensor] = None) -> None:
     """out = a @ w.T (+ bias) on the tensor cores (tcgen05).  a: [M, K] bf16, w: [N, K] bf16;
     out: bf16 (OUT_SAME) or float32 (OUT_F32 store, OUT_ADD_F32 add), or, with OUT_SWIGLU,
-    bf16 [M, N/2] = silu(even columns) * odd columns of the product.  force_splits: 0 = the
+    bf16 [M, N/2] = silu(even columns) * odd columns of the product, or, with OUT_GELU, bf16 [M, N] = the tanh form
+    of gelu of the product, computed in 32-bit from the accumulator.  force_splits: 0 = the
     kernel's own choice of K parts; 1 to 8 = as given.
 
     An RMSNorm around the product can ride along.  ``row_sumsq`` [M, pieces] float32 with
@@ -914,7 +922,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int,
         assert N % 2 == 0 and out.shape == (M, N // 2) and out.dtype == torch.bfloat16
     else:
         assert out.shape == (M, N)
-        assert out.dtype == (torch.bfloat16 if out_mode == OUT_SAME else torch.float32)
+        assert out.dtype == (torch.bfloat16 if out_mode in (OUT_SAME, OUT_GELU) else torch.float32)
     if bias is not None:
         _need(bias, "bias", torch.float32)
         assert bias.numel() == N
@@ -1249,8 +1257,9 @@ def attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
                          cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, kv_lens: torch.Tensor, q_lens,
                          out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                          window: int = 0, tile_order: Optional[torch.Tensor] = None, sink: bool = False,
-                         gate: Optional[torch.Tensor] = None, softcap: float = 0.0, keep_first: int = 0) -> None:
-    """The same as ``attention_prefill`` on tcgen05 tensor cores (head size 64 or 128).  The cache
+                         gate: Optional[torch.Tensor] = None, softcap: float = 0.0, keep_first: int = 0, chunk: int = 0) -> None:
+    """The same as ``attention_prefill`` on tcgen05 tensor cores (head size 64 or 128).  ``chunk`` > 0 (instead of a
+    window): a query at position p sees positions [p - p % chunk, p].  The cache
     pools must hold finite values everywhere (the cache zero-fills them when it allocates them).
     ``tile_order``: what ``prefill_tile_order`` made for this step (the blocks then start heaviest first)."""
     _need(q, "q", torch.bfloat16, contiguous=False); _need(k_pool, "k_pool", torch.bfloat16)
@@ -1266,12 +1275,46 @@ def attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
         assert tile_order.numel() == 2 * tiles
     ldq = q.stride(0) if q.shape[0] > 1 else max(q.stride(0), num_heads * head_dim)
     gptr, ldg = _gate_args(gate, q.shape[0], num_heads * head_dim, 16)
-    _check(library().rl_attention_prefill_tc_masked(
+    _check(library().rl_attention_prefill_tc_shaped(
         q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0], page_table.data_ptr(),
         page_table.shape[1], cu_seqlens.data_ptr(), seq_slots.data_ptr(), kv_lens.data_ptr(), B, tiles, q.shape[0],
         out.data_ptr(), out.stride(0), num_heads, num_kv_heads, head_dim, float(scale), int(window),
         _tc_error_word(q.device).data_ptr(), _ptr(tile_order), int(bool(sink)), gptr, ldg, float(softcap or 0.0),
-        int(keep_first or 0), _stream()), "rl_attention_prefill_tc")
+        int(keep_first or 0), int(chunk or 0), _stream()), "rl_attention_prefill_tc")
+    _count()
+
+
+def attention_shared_key_supported(dtype: torch.dtype, num_heads: int, key_dim: int, value_dim: int) -> bool:
+    return dtype == torch.bfloat16 and bool(library().rl_attention_shared_key_supported(num_heads, key_dim, value_dim))
+
+
+def attention_shared_key(q: torch.Tensor, k_pool: torch.Tensor, page_table: torch.Tensor, cu_seqlens: torch.Tensor,
+                         seq_slots: torch.Tensor, kv_lens: torch.Tensor, q_lens, out: torch.Tensor, num_heads: int,
+                         key_dim: int, value_dim: int, scale: float, window: int = 0,
+                         gate: Optional[torch.Tensor] = None) -> None:
+    """All query heads over ONE cached row a position whose first ``value_dim`` elements are the value (tensor cores,
+    prompt portions and single tokens).  q: [M, >= H * key_dim] bf16; k_pool: [pages, 1, PAGE_SIZE, key_dim]; out:
+    [M, H * value_dim]; ``gate`` [M, H]: head h's output is multiplied by sigmoid(gate[m, h])."""
+    _need(q, "q", torch.bfloat16, contiguous=False); _need(k_pool, "k_pool", torch.bfloat16); _need(out, "out", torch.bfloat16)
+    _need(page_table, "page_table", torch.int32); _need(cu_seqlens, "cu_seqlens", torch.int32)
+    _need(seq_slots, "seq_slots", torch.int32); _need(kv_lens, "kv_lens", torch.int32)
+    B, M = len(q_lens), q.shape[0]
+    assert cu_seqlens.numel() == B + 1 and seq_slots.numel() == B and kv_lens.numel() == B
+    assert M == sum(q_lens) and q.stride(1) == 1 and k_pool.shape[1:] == (1, PAGE_SIZE, key_dim), k_pool.shape
+    assert out.shape == (M, num_heads * value_dim)
+    per_tile = 16 // min(num_heads, 16)
+    one_each = all(n == 1 for n in q_lens)
+    tiles = B if one_each else sum(-(-n // per_tile) for n in q_lens)
+    ldg = 0
+    if gate is not None:
+        _need(gate, "gate", torch.bfloat16, contiguous=False)
+        assert gate.shape == (M, num_heads) and gate.stride(1) == 1
+        ldg = gate.stride(0) if M > 1 else num_heads
+    ldq = q.stride(0) if M > 1 else max(q.stride(0), num_heads * key_dim)
+    _check(library().rl_attention_shared_key(
+        q.data_ptr(), ldq, k_pool.data_ptr(), page_table.data_ptr(), page_table.shape[1], cu_seqlens.data_ptr(),
+        seq_slots.data_ptr(), kv_lens.data_ptr(), B, tiles, int(one_each), out.data_ptr(), out.stride(0), _ptr(gate), ldg,
+        num_heads, key_dim, value_dim, float(scale), int(window or 0), _stream()), "rl_attention_shared_key")
     _count()
 
 
@@ -1291,23 +1334,32 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
     itself.  ``values_in_keys``: the values are the front part of the key rows (any-shape kernel)."""
     if chunk and window:
         raise KernelError("a chunked mask and a sliding window exclude one another")
-    if values_in_keys or gate_per_head or chunk:
+    if (values_in_keys and num_kv_heads == 1 and (gate is None or gate_per_head) and not (sink or softcap or keep_first or chunk)
+            and attention_shared_key_supported(q.dtype, num_heads, head_dim, head_dim if value_dim is None else value_dim)
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
+        # all heads over one cached row whose front is the value: one kernel for prompt portions and single tokens
+        attention_shared_key(q, k_pool, page_table, step.cu_seqlens, step.seq_slots, step.kv_lens, step.q_lens, out,
+                             num_heads, head_dim, head_dim if value_dim is None else value_dim, scale, window, gate=gate)
+        return
+    if values_in_keys or gate_per_head:
         attention_simt(q, k_pool, v_pool, page_table, step.slot_of_token, step.positions, out,
                        num_heads, num_kv_heads, head_dim, scale, window, value_dim=value_dim, sink=sink, gate=gate,
                        softcap=softcap, keep_first=keep_first, chunk=chunk, values_in_keys=values_in_keys,
                        gate_per_head=gate_per_head)
         return
-    masked = bool(softcap or (keep_first and window))
+    # the decode kernel and its plans take a chunked mask as a negative window
+    dec_window = -int(chunk) if chunk else int(window)
+    masked = bool(softcap or (keep_first and window) or chunk)
     tc_prefill = (not step.is_decode and attention_prefill_tc_supported(q.dtype, num_heads, num_kv_heads, head_dim)
                   and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
                   and (gate is None or (gate.data_ptr() % 16 == 0 and gate.stride(0) % 8 == 0)))
     if (value_dim is not None and value_dim != head_dim) or (masked and not tc_prefill and not (
             step.is_decode and attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim))):
-        # soft-capped scores and kept first tokens: the any-shape kernel, the decode kernel and the tcgen05 prompt
-        # kernel have them (the mma.sync prompt kernel does not)
+        # soft-capped scores, kept first tokens and chunked masks: the any-shape kernel, the decode kernel and the
+        # tcgen05 prompt kernel have them (the mma.sync prompt kernel does not)
         attention_simt(q, k_pool, v_pool, page_table, step.slot_of_token, step.positions, out,
                        num_heads, num_kv_heads, head_dim, scale, window, value_dim=value_dim, sink=sink, gate=gate,
-                       softcap=softcap, keep_first=keep_first)
+                       softcap=softcap, keep_first=keep_first, chunk=chunk)
         return
     if step.is_decode and attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim):
         splits = decode_splits(q.shape[0], num_kv_heads)
@@ -1319,22 +1371,22 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
             order = None
             derived = getattr(step, "derived", None)
             if cluster == 1 and derived is not None and decode_order_wanted(q.shape[0], num_kv_heads, head_dim):
-                order = derived.get(("decode_order", int(window)))
+                order = derived.get(("decode_order", dec_window))
                 if order is None:
-                    order = derived[("decode_order", int(window))] = decode_order(step.seq_slots, step.kv_lens, window)
+                    order = derived[("decode_order", dec_window)] = decode_order(step.seq_slots, step.kv_lens, dec_window)
             attention_decode(q, k_pool, v_pool, page_table, step.seq_slots, step.kv_lens, out,
-                             num_heads, num_kv_heads, head_dim, scale, window, num_splits=cluster, plan=order,
+                             num_heads, num_kv_heads, head_dim, scale, dec_window, num_splits=cluster, plan=order,
                              cluster=cluster > 1, sink=sink, gate=gate, softcap=softcap, keep_first=keep_first)
             return
         plan = None
         derived = getattr(step, "derived", None)     # what layers of one step share
         if splits > 1 and q.shape[0] > 1 and derived is not None:
-            key = ("decode_plan", int(window), splits)
+            key = ("decode_plan", dec_window, splits)
             plan = derived.get(key)
             if plan is None:
-                plan = derived[key] = decode_plan(step.seq_slots, step.kv_lens, window, splits)
+                plan = derived[key] = decode_plan(step.seq_slots, step.kv_lens, dec_window, splits)
         attention_decode(q, k_pool, v_pool, page_table, step.seq_slots, step.kv_lens, out,
-                         num_heads, num_kv_heads, head_dim, scale, window, num_splits=splits, plan=plan, sink=sink, gate=gate,
+                         num_heads, num_kv_heads, head_dim, scale, dec_window, num_splits=splits, plan=plan, sink=sink, gate=gate,
                          softcap=softcap, keep_first=keep_first)
         return
     if tc_prefill:
@@ -1346,15 +1398,15 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
                 order = derived["prefill_tile_order"] = prefill_tile_order(step.q_lens, step.kv_lens_host, q.device)
         attention_prefill_tc(q, k_pool, v_pool, page_table, step.cu_seqlens, step.seq_slots, step.kv_lens,
                              step.q_lens, out, num_heads, num_kv_heads, head_dim, scale, window, tile_order=order,
-                             sink=sink, gate=gate, softcap=softcap, keep_first=keep_first)
+                             sink=sink, gate=gate, softcap=softcap, keep_first=keep_first, chunk=chunk)
         return
-    if not step.is_decode and attention_prefill_supported(q.dtype, num_heads, num_kv_heads, head_dim) \
+    if not chunk and not step.is_decode and attention_prefill_supported(q.dtype, num_heads, num_kv_heads, head_dim) \
             and (gate is None or (gate.data_ptr() % 4 == 0 and gate.stride(0) % 2 == 0)):
         attention_prefill(q, k_pool, v_pool, page_table, step.cu_seqlens, step.seq_slots, step.kv_lens,
                           step.q_lens, out, num_heads, num_kv_heads, head_dim, scale, window, sink=sink, gate=gate)
         return
     attention_simt(q, k_pool, v_pool, page_table, step.slot_of_token, step.positions, out,
-                   num_heads, num_kv_heads, head_dim, scale, window, sink=sink, gate=gate)
+                   num_heads, num_kv_heads, head_dim, scale, window, sink=sink, gate=gate, chunk=chunk)
 
 
 from .sampling.config import MAX_TOP_K  # noqa: E402  (one definition, host side)

@@ -98,8 +98,11 @@ class DenseMLP(FeedForward):
 
     def forward(self, xn, residual: torch.Tensor, step, _out_mode=OUT_ADD_F32):
         h = torch.empty((xn.shape[0], self.I), dtype=xn.dtype, device=xn.device)
-        linear(xn, self.wup, h, OUT_SAME)
-        K.gelu_tanh(h, h)
+        if xn.dtype == torch.bfloat16 and self.wup.dtype == torch.bfloat16 and K.gemm_tc_supported(xn, self.wup, None):
+            K.gemm_tc(xn, self.wup, h, K.OUT_GELU)         # the activation rides in the product's epilogue
+        else:
+            linear(xn, self.wup, h, OUT_SAME)
+            K.gelu_tanh(h, h)
         return linear(h, self.wdown, residual, _out_mode)
 
 
