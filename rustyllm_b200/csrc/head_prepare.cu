@@ -251,3 +251,63 @@ extern "C" int rl_latent_query(const void* q, int ldq, int dtype, int num_heads,
   RL_LAUNCH_CHECK("rl_latent_query");
   return RL_OK;
 }
+
+// ------------------------------------------------------------------ a product a head, few tokens
+// out[m, a * out_head + n] = sum_k W[a][n][k] * x[m, a * x_head + k]: every head a has a matrix [N, K] of its own
+// and its own K columns of x (H small products as one launch; with few tokens they only stream the weights).
+// A block: 8 output columns of one head (a warp each) for 16 tokens, whose K inputs wait in shared memory as float.
+#define HL_TOKENS 16
+template <typename T>
+__global__ void __launch_bounds__(256)
+heads_linear_kernel(const T* __restrict__ x, int ldx, int x_head, const T* __restrict__ w, T* __restrict__ out, int ldo,
+                    int out_head, int M, int N, int K) {
+  extern __shared__ float hl_x[];          // [HL_TOKENS][K]
+  const int a = blockIdx.y, m0 = blockIdx.z * HL_TOKENS;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < HL_TOKENS * K; i += 256) {
+    const int m = i / K, k = i - m * K;
+    hl_x[i] = m0 + m < M ? rl_ld(x + (size_t)(m0 + m) * ldx + (size_t)a * x_head + k) : 0.f;
+  }
+  __syncthreads();
+  const int n = blockIdx.x * 8 + warp;
+  if (n >= N) return;
+  const T* wrow = w + ((size_t)a * N + n) * K;
+  float acc[HL_TOKENS];
+#pragma unroll
+  for (int m = 0; m < HL_TOKENS; ++m) acc[m] = 0.f;
+  for (int k = lane; k < K; k += 32) {
+    const float wv = rl_ld(wrow + k);
+#pragma unroll
+    for (int m = 0; m < HL_TOKENS; ++m) acc[m] = fmaf(wv, hl_x[m * K + k], acc[m]);
+  }
+  float mine = 0.f;
+#pragma unroll
+  for (int m = 0; m < HL_TOKENS; ++m) {
+    const float v = rl_warp_sum(acc[m]);
+    if (lane == m) mine = v;
+  }
+  if (lane < HL_TOKENS && m0 + lane < M) rl_st(out + (size_t)(m0 + lane) * ldo + (size_t)a * out_head + n, mine);
+}
+
+// x: [M, ldx] with head a's K inputs at columns [a * x_head, a * x_head + K); w: [H, N, K] contiguous; out: [M, ldo]
+// with head a's N outputs at columns [a * out_head, a * out_head + N); all of one dtype, sums in 32-bit.
+extern "C" int rl_heads_linear(const void* x, int ldx, int x_head, const void* w, void* out, int ldo, int out_head, int dtype,
+                               int M, int H, int N, int K, cudaStream_t stream) {
+  RL_REQUIRE(M >= 0 && H > 0 && N > 0 && K > 0 && H <= 65535, "rl_heads_linear: bad sizes");
+  RL_REQUIRE(ldx >= (H - 1) * x_head + K && ldo >= (H - 1) * out_head + N && x_head >= 0 && out_head >= N,
+             "rl_heads_linear: row strides too small for the heads");
+  const size_t smem = (size_t)HL_TOKENS * K * sizeof(float);
+  RL_REQUIRE(smem <= 48 * 1024, "rl_heads_linear: %d inputs a head exceed the %d this kernel holds", K, 48 * 1024 / (HL_TOKENS * 4));
+  if (M == 0) return RL_OK;
+  const dim3 grid((N + 7) / 8, H, (M + HL_TOKENS - 1) / HL_TOKENS);
+  RL_REQUIRE(grid.z <= 65535, "rl_heads_linear: too many tokens (%d) for this kernel", M);
+  if (dtype == RL_F32)
+    heads_linear_kernel<float><<<grid, 256, smem, stream>>>((const float*)x, ldx, x_head, (const float*)w, (float*)out, ldo, out_head, M, N, K);
+  else if (dtype == RL_BF16)
+    heads_linear_kernel<__nv_bfloat16><<<grid, 256, smem, stream>>>((const __nv_bfloat16*)x, ldx, x_head, (const __nv_bfloat16*)w,
+                                                                   (__nv_bfloat16*)out, ldo, out_head, M, N, K);
+  else
+    RL_REQUIRE(false, "rl_heads_linear: unknown dtype %d", dtype);
+  RL_LAUNCH_CHECK("rl_heads_linear");
+  return RL_OK;
+}

@@ -57,6 +57,7 @@ _SIGNATURES = {
     "rl_attention_shared_key_supported": [_c_int, _c_int, _c_int],
     "rl_attention_shared_key": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                                 _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p],
+    "rl_heads_linear": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "rl_embedding_pair": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll,
                           _c_float, _c_ll, _c_ll, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_gelu_tanh": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
@@ -698,6 +699,23 @@ def latent_query(q: torch.Tensor, out: torch.Tensor, num_heads: int, head_dim: i
     _check(library().rl_latent_query(q.data_ptr(), ldq, _dt(q), num_heads, head_dim, rot_dim, positions.data_ptr(),
                                      inv_freq.data_ptr(), int(rotary_dim), int(bool(interleaved)), out.data_ptr(), out.stride(0),
                                      latent_dim, M, _stream()), "rl_latent_query")
+    _count()
+
+
+HEADS_LINEAR_MAX_K = 768      # inputs a head that ``heads_linear`` holds in shared memory
+
+
+def heads_linear(x: torch.Tensor, x_head: int, w: torch.Tensor, out: torch.Tensor, out_head: int) -> None:
+    """A product a head in one launch, for few tokens: out[m, a * out_head + n] = sum_k w[a, n, k] x[m, a * x_head + k].
+    x: [M, >= (H - 1) * x_head + K]; w: [H, N, K]; out: [M, >= (H - 1) * out_head + N]; one dtype, sums in 32-bit."""
+    _need(x, "x", contiguous=False); _need(w, "w", x.dtype); _need(out, "out", x.dtype, contiguous=False)
+    H, N, Kd = w.shape
+    M = x.shape[0]
+    assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == M and Kd <= HEADS_LINEAR_MAX_K
+    ldx = x.stride(0) if M > 1 else x.shape[1]
+    ldo = out.stride(0) if M > 1 else out.shape[1]
+    _check(library().rl_heads_linear(x.data_ptr(), ldx, int(x_head), w.data_ptr(), out.data_ptr(), ldo, int(out_head), _dt(x),
+                                     M, H, N, Kd, _stream()), "rl_heads_linear")
     _count()
 
 

@@ -56,6 +56,8 @@ class LatentAttention(Mixer):
             raise ValueError(f"{self.position.rotary_dim} rotated dimensions exceed the rotary part's {rot_dim}")
         self.w_in = self.wuq = self.wuk = self.wuv = self.wo = self.q_norm_w = self.kv_norm_w = None
 
+    FEW_TOKENS = 64        # up to here a step's per-head products run on the CUDA cores as one launch
+
     def param_specs(self) -> Dict[str, ParamSpec]:
         d, H, hd, rd, vd, n = self.d, self.H, self.hd, self.rd, self.vd, self.names
         sfx = n.get("suffix", ".weight")
@@ -102,12 +104,21 @@ class LatentAttention(Mixer):
         linear(cq, self.wuq, q, OUT_SAME)
         ql = torch.empty((M, H * (r + rd)), dtype=dt, device=dev)       # a head: [Wuk^T q_plain | rot(q_rot)]
         K.latent_query(q, ql, H, hd, rd, r, step.positions, pos.inv_freq, pos.rotary_dim, pos.interleaved)
-        for a in range(H):
-            linear(q[:, a * (hd + rd):a * (hd + rd) + hd], self.wuk[a], ql[:, a * (r + rd):a * (r + rd) + r], OUT_SAME)
+        # a product a head: with few tokens they only stream weights and run as one launch; with many, one tensor-core
+        # product a head
+        few = M <= self.FEW_TOKENS and self.wuk.dtype == dt and self.wuv.dtype == dt
+        if few and hd <= K.HEADS_LINEAR_MAX_K:
+            K.heads_linear(q, hd + rd, self.wuk, ql, r + rd)
+        else:
+            for a in range(H):
+                linear(q[:, a * (hd + rd):a * (hd + rd) + hd], self.wuk[a], ql[:, a * (r + rd):a * (r + rd) + r], OUT_SAME)
         ol = torch.empty((M, H * r), dtype=dt, device=dev)              # a head: its gate * sum_j p_ij c_j
         K.attention(ql, k_pool, k_pool, group.page_table, step, ol, H, 1, r + rd, self.scale, self.window or 0, value_dim=r,
                     gate=u[:, qr + r + rd:] if self.head_gate else None, gate_per_head=self.head_gate, values_in_keys=True)
         o = torch.empty((M, H * vd), dtype=dt, device=dev)
-        for a in range(H):
-            linear(ol[:, a * r:(a + 1) * r], self.wuv[a * vd:(a + 1) * vd], o[:, a * vd:(a + 1) * vd], OUT_SAME)
+        if few and r <= K.HEADS_LINEAR_MAX_K:
+            K.heads_linear(ol, r, self.wuv.view(H, vd, r), o, vd)
+        else:
+            for a in range(H):
+                linear(ol[:, a * r:(a + 1) * r], self.wuv[a * vd:(a + 1) * vd], o[:, a * vd:(a + 1) * vd], OUT_SAME)
         return linear(o, self.wo, residual, _out_mode)

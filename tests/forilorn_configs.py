@@ -145,8 +145,8 @@ def random_config(seed):
            "norm": {"eps": rng.choice([1e-6, 1e-5, 1e-3])}, "residual_mult": rng.choice([0.3, 0.5, 1.0, 1.4]),
            "embedding": {"scale": rng.choice([1.0, 4.0, 9.5])}, "layers": layers}
     if rng.random() < 0.7:
-        cfg["embedding"]["bigram"] = {"buckets": rng.choice([1, 7, 64, 509]), "mul_prev": rng.choice([0, 1, 31, 1000003]),
-                                      "mul_cur": rng.choice([0, 1, 17, 999983])}
+        cfg["embedding"]["bigram"] = {"buckets": rng.choice([1, 7, 64, 499]), "mul_prev": rng.choice([0, 1, 29, 1000003]),
+                                      "mul_cur": rng.choice([0, 1, 19, 999983])}
     return cfg
 
 

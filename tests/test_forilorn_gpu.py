@@ -101,7 +101,7 @@ def inv_freq(dims, base):
 
 # =========================================================================== mechanisms alone
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("buckets,mul_prev,mul_cur", [(61, 7, 13), (1, 1, 1), (509, 1000003, 999983), (5, 0, 3), (None, 0, 0)])
+@pytest.mark.parametrize("buckets,mul_prev,mul_cur", [(61, 7, 13), (1, 1, 1), (499, 1000003, 999983), (5, 0, 3), (None, 0, 0)])
 def test_scaled_pair_embedding_across_steps(dtype, buckets, mul_prev, mul_cur):
     """Two sequences packed in every step and cut differently; the previous token crosses the cuts through the slot's
     state, a sequence's first token takes the row behind the buckets, and a slot that is used again starts anew."""
@@ -704,3 +704,20 @@ def test_command_line_generates_benchmarks_and_times_kernels(dirs, capsys):
         rows = {r["name"]: r for r in json.loads(capsys.readouterr().out)["rows"]}
         for n in names:
             assert rows[n]["avg_us"] > 0, n
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,H,N,K,x_head,out_head", [(1, 3, 32, 24, 32, 40), (17, 16, 512, 128, 192, 576), (64, 4, 48, 96, 96, 48), (33, 1, 7, 5, 5, 9)])
+def test_a_product_a_head_in_one_launch(dtype, M, H, N, K, x_head, out_head):
+    from rustyllm_b200 import kernels as K_
+    torch.manual_seed(M + N)
+    x = rounded(torch.randn(M, (H - 1) * x_head + K + 3, dtype=F64), dtype)
+    w = rounded(torch.randn(H, N, K, dtype=F64) / math.sqrt(K), dtype)
+    out = torch.full((M, (H - 1) * out_head + N + 2), 7.0, dtype=tdt(dtype), device=DEV)
+    K_.heads_linear(x.to(tdt(dtype)).to(DEV), x_head, w.to(tdt(dtype)).to(DEV), out, out_head)
+    K_.check_device_errors()
+    got = out.double().cpu()
+    for a in range(H):
+        ref = x[:, a * x_head:a * x_head + K] @ w[a].T
+        torch.testing.assert_close(got[:, a * out_head:a * out_head + N], ref, **tol(dtype))
+    assert (got[:, (H - 1) * out_head + N:] == 7.0).all()
