@@ -84,12 +84,12 @@ def forilorn_config(s: dict, window: int = 1024) -> dict:
     d, H, hd = s["width"], s["heads"], s["dim"]
     plain = {"heads": H, "kv_heads": s["kv_heads"], "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": window},
              "rot": {"base": 10000.0, "dims": hd}}
-    lat = {"heads": H, "dim": hd, "rot_dim": 64, "vdim": hd, "q_rank": 3 * d // 8, "kv_rank": d // 4, "scale": (hd + 64) ** -0.5,
+    lat = {"heads": H, "dim": hd, "rot_dim": 64, "vdim": hd, "q_rank": min(1536, 3 * d // 8), "kv_rank": min(512, d // 4), "scale": (hd + 64) ** -0.5,
            "mask": {"size": window}, "rot": {"base": 10000.0, "dims": 64}}
     layers = [{"type": "latent_attention" if i % 4 == 2 else "attention", "mixer": dict(lat if i % 4 == 2 else plain),
                "mlp": {"kind": "dense", "ff": s["ff"]}} for i in range(s["layers"])]
     return {"architecture": "Forilorn", "vocab": s["vocab"], "width": d, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
-            "embedding": {"scale": d ** 0.5, "bigram": {"buckets": 65536, "mul_prev": 31, "mul_cur": 17}}, "layers": layers}
+            "embedding": {"scale": d ** 0.5, "bigram": {"buckets": 65536, "mul_prev": 1000003, "mul_cur": 999983}}, "layers": layers}
 
 
 def measure(config: dict, prompt: int, batches: List[int], context: int, steps: int, warmup: int) -> Dict[str, float]:

@@ -56,7 +56,9 @@ _SIGNATURES = {
                                  _c_int, _c_void_p, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "rl_attention_shared_key_supported": [_c_int, _c_int, _c_int],
     "rl_attention_shared_key": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
-                                _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p],
+                                _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p,
+                                _c_void_p],
+    "rl_attention_shared_key_block_tokens": [_c_int, _c_int, _c_int],
     "rl_heads_linear": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "rl_embedding_pair": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll,
                           _c_float, _c_ll, _c_ll, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
@@ -1320,19 +1322,29 @@ def attention_shared_key(q: torch.Tensor, k_pool: torch.Tensor, page_table: torc
     assert cu_seqlens.numel() == B + 1 and seq_slots.numel() == B and kv_lens.numel() == B
     assert M == sum(q_lens) and q.stride(1) == 1 and k_pool.shape[1:] == (1, PAGE_SIZE, key_dim), k_pool.shape
     assert out.shape == (M, num_heads * value_dim)
-    per_tile = 16 // min(num_heads, 16)
     one_each = all(n == 1 for n in q_lens)
-    tiles = B if one_each else sum(-(-n // per_tile) for n in q_lens)
+    per_block = int(library().rl_attention_shared_key_block_tokens(num_heads, key_dim, int(one_each)))
+    tiles = B if one_each else sum(-(-n // per_block) for n in q_lens)
     ldg = 0
     if gate is not None:
         _need(gate, "gate", torch.bfloat16, contiguous=False)
         assert gate.shape == (M, num_heads) and gate.stride(1) == 1
         ldg = gate.stride(0) if M > 1 else num_heads
     ldq = q.stride(0) if M > 1 else max(q.stride(0), num_heads * key_dim)
+    # single tokens of few sequences: a sequence's key blocks in several runs, so that the step fills the GPU.  The
+    # count depends on the batch's size and the window alone (a captured step keeps its grid).
+    groups = -(-num_heads // 16)
+    splits, part = 1, None
+    if one_each:
+        splits = max(1, min(8, num_sms() // (B * groups)))
+        if window:
+            splits = min(splits, -(-int(window) // PAGE_SIZE) + 1)
+        if splits > 1:
+            part = torch.empty((B * groups * splits * 16 * (value_dim + 2),), dtype=torch.float32, device=q.device)
     _check(library().rl_attention_shared_key(
         q.data_ptr(), ldq, k_pool.data_ptr(), page_table.data_ptr(), page_table.shape[1], cu_seqlens.data_ptr(),
         seq_slots.data_ptr(), kv_lens.data_ptr(), B, tiles, int(one_each), out.data_ptr(), out.stride(0), _ptr(gate), ldg,
-        num_heads, key_dim, value_dim, float(scale), int(window or 0), _stream()), "rl_attention_shared_key")
+        num_heads, key_dim, value_dim, float(scale), int(window or 0), splits, _ptr(part), _stream()), "rl_attention_shared_key")
     _count()
 
 

@@ -721,3 +721,56 @@ def test_a_product_a_head_in_one_launch(dtype, M, H, N, K, x_head, out_head):
         ref = x[:, a * x_head:a * x_head + K] @ w[a].T
         torch.testing.assert_close(got[:, a * out_head:a * out_head + N], ref, **tol(dtype))
     assert (got[:, (H - 1) * out_head + N:] == 7.0).all()
+
+
+@pytest.mark.parametrize("H,r,rd", [(16, 64, 32), (4, 96, 16), (3, 32, 16)])
+@pytest.mark.parametrize("window", [None, 130])
+def test_heads_over_one_cached_row_with_unequal_sequences_in_one_step(H, r, rd, window):
+    """Five sequences of unequal lengths as one prompt step (blocks of two tiles that end inside a sequence), then four
+    single-token steps of all of them (a sequence's keys in several runs, some of them empty), each against the
+    sequence alone in the plain implementation."""
+    from rustyllm_b200 import kernels as K
+    from rustyllm_b200.cache.sequence_cache import KVNeed, SequenceCache
+    from rustyllm_b200.engine.step import StepState
+    dtype, extra = "bfloat16", 4
+    lens = [200, 37, 1, 129, 64]
+    torch.manual_seed(H + r)
+    scale = 2.0 / math.sqrt(r + rd)
+    ql = [rounded(torch.randn(n + extra, H * (r + rd), dtype=F64), dtype) for n in lens]
+    rows = [rounded(torch.randn(n + extra, r + rd, dtype=F64), dtype) for n in lens]
+    gate = [rounded(2.0 * torch.randn(n + extra, H, dtype=F64), dtype) for n in lens]
+    cache = SequenceCache([KVNeed(1, r + rd, window, 0)], [None], 64 * 12, tdt(dtype), DEV, max_slots=6)
+    cache.alloc_slot()
+    slots = [cache.alloc_slot() for _ in lens]
+    group, layer = cache.kv_entry(0)
+    got = [[] for _ in lens]
+    at = [0] * len(lens)
+    for cnts in [lens] + [[1] * len(lens)] * extra:
+        cache.prepare(slots, cnts)
+        pool = group.k_pool(layer)
+        for b, (s, a, c) in enumerate(zip(slots, at, cnts)):
+            pages = group.page_table[s].tolist()
+            for p in range(a, a + c):
+                pool[pages[p // 64], 0, p % 64] = rows[b][p].to(tdt(dtype)).to(DEV)
+        M = sum(cnts)
+        kv = [a + c for a, c in zip(at, cnts)]
+        cu = [0]
+        for c in cnts:
+            cu.append(cu[-1] + c)
+        st = StepState(M, len(lens), i32([0] * M), i32([p for a, c in zip(at, cnts) for p in range(a, a + c)]),
+                       i32([s for s, c in zip(slots, cnts) for _ in range(c)]), i32(cu), i32(slots), i32(kv), i32([]), list(cnts), kv,
+                       max(cnts), max(kv), all(c == 1 for c in cnts))
+        q = torch.cat([ql[b][a:a + c] for b, (a, c) in enumerate(zip(at, cnts))]).to(tdt(dtype)).to(DEV).contiguous()
+        gt = torch.cat([gate[b][a:a + c] for b, (a, c) in enumerate(zip(at, cnts))]).to(tdt(dtype)).to(DEV).contiguous()
+        out = torch.empty((M, H * r), dtype=tdt(dtype), device=DEV)
+        K.attention(q, pool, pool, group.page_table, st, out, H, 1, r + rd, scale, window or 0, value_dim=r, gate=gt,
+                    gate_per_head=True, values_in_keys=True)
+        o = out.double().cpu()
+        for b, c in enumerate(cnts):
+            got[b].append(o[cu[b]:cu[b] + c])
+        cache.commit(slots, cnts)
+        at = kv
+    K.check_device_errors()
+    for b in range(len(lens)):
+        ref = plain_latent_scan(H, r, rd, window, scale, ql[b], rows[b], gate[b])
+        torch.testing.assert_close(torch.cat(got[b]), ref, rtol=2e-2, atol=2e-2)
