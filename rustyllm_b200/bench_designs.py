@@ -13,9 +13,9 @@ uses together with the shared one are as wide as the dense feed-forward), vocabu
                  four with linear attention with decay; every feed-forward 16 experts in 4 groups (2 kept), 4 a token,
                  each a quarter of the dense width; a per-layer token input of 256 columns
   forilorn       post-norm layers with a scaled stream; three in four with grouped-query attention whose values are its
-                 keys (no value projection), rotated neighbours, unit-size q and k heads, blocks of 1,024 positions as the
+                 keys (no value projection), rotated neighbours, unit-size q and k heads, blocks of 2,048 positions as the
                  mask and an output gate an element; one in four with attention through latents (queries 3/8 of the
-                 width, keys and values 1/4 of it plus a rotary key part of 64 for all heads, a window of 1,024, a gate
+                 width, at most 1,536; keys and values 1/4 of it, at most 512, plus a rotary key part of 64 for all heads, a window of 1,024, a gate
                  a head); dense gelu feed-forwards; a hashed pair table of 65,536 rows beside the embedding; tied head
 ``--kernels`` times the Mogutar design's own kernels alone at the sizes of a layer (a JSON line a kernel, with the
 bytes it must move and their share of the measured copy bandwidth).
@@ -82,7 +82,8 @@ def mogutar_config(s: dict, window: int = 1024) -> dict:
 
 def forilorn_config(s: dict, window: int = 1024) -> dict:
     d, H, hd = s["width"], s["heads"], s["dim"]
-    plain = {"heads": H, "kv_heads": s["kv_heads"], "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": window},
+    # blocks of twice the window: the 2,048-token prompt and the single tokens behind 1,024 see what the other models' see
+    plain = {"heads": H, "kv_heads": s["kv_heads"], "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": 2 * window},
              "rot": {"base": 10000.0, "dims": hd}}
     lat = {"heads": H, "dim": hd, "rot_dim": 64, "vdim": hd, "q_rank": min(1536, 3 * d // 8), "kv_rank": min(512, d // 4), "scale": (hd + 64) ** -0.5,
            "mask": {"size": window}, "rot": {"base": 10000.0, "dims": 64}}
@@ -283,7 +284,7 @@ def kernel_times(sizes: List[str], prompt: int = 2048, batch: int = 64, runs: in
 def forilorn_kernel_times(sizes: List[str], prompt: int = 2048, batch: int = 64, context: int = 1024, mask: int = 1024,
                           runs: int = 20) -> List[dict]:
     """The Forilorn design's kernels alone beside the like kernel of the Mosurax design, bfloat16, at a layer's sizes:
-    ``prompt`` tokens of one sequence, and one token of each of ``batch`` sequences that hold ``context`` tokens.  A
+    ``prompt`` tokens of one sequence, and one token of each of ``batch`` sequences that hold ``context`` tokens with it.  A
     row gives the bytes the kernel must move and the operations it must do, the time both would take at the measured
     copy bandwidth and matrix throughput, and the larger of the two over the measured time (``of_roofline``)."""
     import json as _json
@@ -341,9 +342,10 @@ def forilorn_kernel_times(sizes: List[str], prompt: int = 2048, batch: int = 64,
     for name in sizes:
         s = SIZES[name]
         d, H, G, hd, ff = s["width"], s["heads"], s["kv_heads"], s["dim"], s["ff"]
-        r, rd, qr = d // 4, 64, 3 * d // 8
+        r, rd, qr = min(512, d // 4), 64, min(1536, 3 * d // 8)
         scale = hd ** -0.5
-        for what, B, held, cnt in (("prompt", 1, 0, prompt), ("single tokens", batch, context, 1)):
+        # the single token is the last of a block of the mask: it sees ``mask`` keys under either kind of mask
+        for what, B, held, cnt in (("prompt", 1, 0, prompt), ("single tokens", batch, context - 1, 1)):
             M = B * cnt
             pages = 64 * (-(-(held + cnt) // 64) + 1) * B
             seen = lambda lo: sum(p - lo(p) + 1 for p in range(held, held + cnt)) * B      # (query, key) pairs

@@ -96,6 +96,80 @@ qk_rotate_unit_kernel(const T* __restrict__ u, int ldu, T* __restrict__ q_out, i
   }
 }
 
+// The same for neighbouring pairs (2i, 2i + 1) with even widths and strides: a lane owns whole pairs (elements
+// 2 lane + 64 e and the next), so a pair is one load and one store of twice the width, its partner needs no shared
+// memory, and an angle's sine and cosine are computed once a pair.
+__device__ __forceinline__ float2 hp_ld2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 hp_ld2(const __nv_bfloat16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+__device__ __forceinline__ void hp_st2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void hp_st2(__nv_bfloat16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); }
+
+template <typename T>
+__global__ void __launch_bounds__(HP_WARPS * 32)
+qk_rotate_unit_pairs_kernel(const T* __restrict__ u, int ldu, T* __restrict__ q_out, int ldq, const int* __restrict__ positions,
+                            const int* __restrict__ slot_of_token, const int* __restrict__ page_table, int max_pages,
+                            const float* __restrict__ inv_freq, int rot, int unit_norm, float eps, int H, int G, int hd,
+                            int value_from_key, T* __restrict__ k_pool, T* __restrict__ v_pool) {
+  constexpr int NP = HP_MAX_W / 64;
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  const int m = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hs = blockIdx.y * HP_WARPS + warp;          // head: queries first, then keys
+  if (hs >= H + G) return;
+  const bool is_q = hs < H;
+  const int pos = positions[m];
+  const T* src = u + (size_t)m * ldu + (size_t)hs * hd;
+  float a[NP], b[NP];
+#pragma unroll
+  for (int e = 0; e < NP; ++e) {
+    const int i = 2 * lane + 64 * e;
+    const float2 v = i < hd ? hp_ld2(src + i) : make_float2(0.f, 0.f);
+    a[e] = v.x; b[e] = v.y;
+  }
+  T* kdst = nullptr;
+  if (!is_q && k_pool != nullptr) {
+    const int slot = slot_of_token[m];
+    const int page = page_table[(size_t)slot * max_pages + pos / RL_PAGE];
+    const size_t row = (((size_t)page * G + (hs - H)) * RL_PAGE + pos % RL_PAGE) * hd;
+    kdst = k_pool + row;
+    if (value_from_key) {
+      T* vdst = v_pool + row;
+#pragma unroll
+      for (int e = 0; e < NP; ++e) {
+        const int i = 2 * lane + 64 * e;
+        if (i < hd) hp_st2(vdst + i, a[e], b[e]);
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < NP; ++e) {
+    const int i = 2 * lane + 64 * e;
+    if (i < rot) {
+      float sn, cs;
+      sincosf((float)pos * inv_freq[i >> 1], &sn, &cs);
+      const float x = a[e], y = b[e];
+      a[e] = x * cs - y * sn;
+      b[e] = y * cs + x * sn;
+    }
+  }
+  if (unit_norm) {
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < NP; ++e) ss = fmaf(b[e], b[e], fmaf(a[e], a[e], ss));     // elements beyond hd are 0
+    const float r = 1.0f / sqrtf(rl_warp_sum(ss) / (float)hd + eps);
+#pragma unroll
+    for (int e = 0; e < NP; ++e) { a[e] *= r; b[e] *= r; }
+  }
+  T* dst = is_q ? q_out + (size_t)m * ldq + (size_t)hs * hd : kdst;
+  if (dst == nullptr) return;
+#pragma unroll
+  for (int e = 0; e < NP; ++e) {
+    const int i = 2 * lane + 64 * e;
+    if (i < hd) hp_st2(dst + i, a[e], b[e]);
+  }
+}
+
 // u [M, ldu]: columns [0, H*hd) the query heads, [H*hd, (H+G)*hd) the key heads.  q_out [M, ldq] (may be u itself:
 // a head is read whole before it is written).  k_pool, v_pool: [pages, G, RL_PAGE, hd]; k_pool null: nothing is
 // cached.  v_pool is needed (and written) only with value_from_key.
@@ -112,7 +186,19 @@ extern "C" int rl_qk_rotate_unit(const void* u, int ldu, void* q_out, int ldq, i
   RL_REQUIRE(k_pool == nullptr || !value_from_key || v_pool != nullptr, "rl_qk_rotate_unit: values from keys need a value pool");
   if (num_tokens == 0) return RL_OK;
   const dim3 grid(num_tokens, (num_heads + num_kv_heads + HP_WARPS - 1) / HP_WARPS);
-  if (dtype == RL_F32)
+  // neighbouring pairs (or no rotation at all) on even sizes and addresses of whole pairs: a pair a load
+  const uintptr_t two = dtype == RL_F32 ? 8 : 4;
+  const bool pairs = (interleaved || rotary_dim == 0) && head_dim % 2 == 0 && ldu % 2 == 0 && ldq % 2 == 0 &&
+                     (uintptr_t)u % two == 0 && (uintptr_t)q_out % two == 0 && (uintptr_t)k_pool % two == 0 && (uintptr_t)v_pool % two == 0;
+  if (pairs && dtype == RL_F32)
+    rl_launch_pdl(qk_rotate_unit_pairs_kernel<float>, grid, HP_WARPS * 32, 0, stream, (const float*)u, ldu, (float*)q_out, ldq, positions,
+                  slot_of_token, page_table, max_pages, inv_freq, rotary_dim, unit_norm, eps, num_heads, num_kv_heads,
+                  head_dim, value_from_key, (float*)k_pool, (float*)v_pool);
+  else if (pairs && dtype == RL_BF16)
+    rl_launch_pdl(qk_rotate_unit_pairs_kernel<__nv_bfloat16>, grid, HP_WARPS * 32, 0, stream, (const __nv_bfloat16*)u, ldu,
+                  (__nv_bfloat16*)q_out, ldq, positions, slot_of_token, page_table, max_pages, inv_freq, rotary_dim,
+                  unit_norm, eps, num_heads, num_kv_heads, head_dim, value_from_key, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool);
+  else if (dtype == RL_F32)
     rl_launch_pdl(qk_rotate_unit_kernel<float>, grid, HP_WARPS * 32, 0, stream, (const float*)u, ldu, (float*)q_out, ldq, positions,
                   slot_of_token, page_table, max_pages, inv_freq, rotary_dim, interleaved, unit_norm, eps, num_heads, num_kv_heads,
                   head_dim, value_from_key, (float*)k_pool, (float*)v_pool);

@@ -144,7 +144,7 @@ def test_scaled_pair_embedding_across_steps(dtype, buckets, mul_prev, mul_cur):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,hd,dims,base", [(4, 2, 16, 8, 100.0), (4, 1, 64, 64, 10000.0), (2, 2, 128, 32, 1.0e6), (6, 3, 18, 0, 1.0),
-                                               (3, 3, 50, 50, 200000.0)])
+                                               (3, 3, 50, 50, 200000.0), (2, 1, 17, 8, 100.0)])
 def test_rotation_of_neighbours_then_unit_heads_values_from_keys(dtype, H, G, hd, dims, base):
     """q and k heads: neighbouring pairs of the first ``dims`` dimensions turn by the position, then the head is divided
     by its root mean square; the keys' pages take that, the values' pages the keys as they were projected.  Positions

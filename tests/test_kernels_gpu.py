@@ -1165,10 +1165,10 @@ def test_kernels_refuse_what_they_cannot_do():
     k = K()
     with pytest.raises(k.KernelError, match="CUDA tensors only"):
         k.swiglu(torch.zeros(2, 4), torch.zeros(2, 2))
-    q = torch.zeros(1, 2 * 300, device=DEV)
+    q = torch.zeros(1, 2 * 1100, device=DEV)      # the any-shape kernel takes heads of up to 1,024
     with pytest.raises(k.KernelError, match="head_dim"):
-        k.attention_simt(q, torch.zeros(1, 2, PAGE, 300, device=DEV), torch.zeros(1, 2, PAGE, 300, device=DEV),
+        k.attention_simt(q, torch.zeros(1, 2, PAGE, 1100, device=DEV), torch.zeros(1, 2, PAGE, 1100, device=DEV),
                          torch.zeros(1, 1, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
-                         torch.zeros(1, dtype=torch.int32, device=DEV), torch.zeros(1, 600, device=DEV), 2, 2, 300, 1.0)
+                         torch.zeros(1, dtype=torch.int32, device=DEV), torch.zeros(1, 2200, device=DEV), 2, 2, 1100, 1.0)
     with pytest.raises(k.KernelError, match="not handled"):
         k.swiglu(torch.zeros(2, 4, dtype=torch.float16, device=DEV), torch.zeros(2, 2, dtype=torch.float16, device=DEV))
