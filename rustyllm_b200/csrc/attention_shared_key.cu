@@ -76,7 +76,7 @@ attention_shared_key_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const 
                             const int* __restrict__ seq_slots, const int* __restrict__ kv_lens, int num_seqs,
                             int one_token_each, __nv_bfloat16* __restrict__ out, int ldo,
                             const __nv_bfloat16* __restrict__ gate, int ldg, int H, int DK, int DV, float scale_log2e,
-                            int window, int splits, float* __restrict__ part) {
+                            int window, int splits, float* __restrict__ part, int head_tiles) {
   extern __shared__ __align__(128) uint8_t sk_smem[];
   __shared__ int s_where[2];
   const SkLayout L = sk_layout(DK, MT);
@@ -102,11 +102,13 @@ attention_shared_key_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const 
   if (b >= num_seqs) return;                   // the grid is sized exactly; defensive
   const int row0 = cu_seqlens[b], q_len = cu_seqlens[b + 1] - row0, kv_len = kv_lens[b];
   const int start_pos = kv_len - q_len;
-  const int blk_tok0 = s_where[1] * MT * TOK;                         // the block's first token
-  const int blk_toks = min(MT * TOK, q_len - blk_tok0);
-  const int tok0 = blk_tok0 + mt * TOK;                                // this tile's
+  // a block's tiles lie along the tokens (prompts) or, with head_tiles, along the head groups of the same tokens
+  const int tok_tiles = head_tiles ? 1 : MT;
+  const int blk_tok0 = s_where[1] * tok_tiles * TOK;                  // the block's first token
+  const int blk_toks = min(tok_tiles * TOK, q_len - blk_tok0);
+  const int tok0 = blk_tok0 + (head_tiles ? 0 : mt) * TOK;             // this tile's
   const int toks_here = max(0, min(TOK, q_len - tok0));
-  const int head0 = blockIdx.y * 16;
+  const int head0 = (head_tiles ? (int)blockIdx.y * MT + mt : (int)blockIdx.y) * 16;
   const int* pages = page_table + (size_t)seq_slots[b] * max_pages;
   const uint32_t smem = (uint32_t)__cvta_generic_to_shared(sk_smem);
   float* s_s = reinterpret_cast<float*>(sk_smem + L.s_off) + mt * SK_ROWS * (SK_KEYS + 4);
@@ -124,12 +126,13 @@ attention_shared_key_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const 
   // unnormalised sums, maximum and denominator to `part` (float [16][DV + 2] a block) for the combining kernel
   float* my_part = nullptr;
   if (splits > 1) {
-    my_part = part + (((size_t)blockIdx.x * gridDim.y + blockIdx.y) * splits + blockIdx.z) * SK_ROWS * (DV + 2);
+    if (head0 < H)                             // (a tile behind the last head group has no rows and no place)
+      my_part = part + (((size_t)blockIdx.x * ((H + 15) / 16) + head0 / 16) * splits + blockIdx.z) * SK_ROWS * (DV + 2);
     const int per = (kb_end - kb_begin + splits - 1) / splits;
     kb_begin += (int)blockIdx.z * per;
     kb_end = min(kb_end, kb_begin + per);
     if (kb_begin >= kb_end) {                  // nothing left for this run: it counts as weight zero
-      if (threadIdx.x < SK_ROWS) { my_part[threadIdx.x * (DV + 2) + DV] = -INFINITY; my_part[threadIdx.x * (DV + 2) + DV + 1] = 0.f; }
+      if (my_part != nullptr && warp == 0 && lane < SK_ROWS) { my_part[lane * (DV + 2) + DV] = -INFINITY; my_part[lane * (DV + 2) + DV + 1] = 0.f; }
       return;
     }
   }
@@ -138,8 +141,9 @@ attention_shared_key_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const 
   // ---- the query tile: row r = (token r / HG, head head0 + r % HG); rows without a token or head are zero ----
   for (int i = threadIdx.x; i < MT * SK_ROWS * pieces_row; i += MT * SK_WARPS * 32) {
     const int r = i / pieces_row, ch = i % pieces_row;               // rows of all tiles: tile r / 16
-    const int rl = r % SK_ROWS;
-    const int tok = (r / SK_ROWS) * TOK + rl / HG, head = head0 + rl % HG;
+    const int rl = r % SK_ROWS, tile = r / SK_ROWS;
+    const int tok = (head_tiles ? 0 : tile * TOK) + rl / HG;
+    const int head = (head_tiles ? (int)blockIdx.y * MT + tile : (int)blockIdx.y) * 16 + rl % HG;
     const uint32_t dst = smem + L.q_off + (uint32_t)(r * ldk * 2 + ch * 16);
     if (rl / HG < TOK && tok < blk_toks && head < H) sk_cp16(dst, q + (size_t)(row0 + blk_tok0 + tok) * ldq + (size_t)head * DK + ch * 8);
     else *reinterpret_cast<uint4*>(sk_smem + L.q_off + r * ldk * 2 + ch * 16) = make_uint4(0u, 0u, 0u, 0u);
@@ -254,7 +258,8 @@ attention_shared_key_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const 
       }
     }
   }
-  if (my_part != nullptr) {
+  if (splits > 1) {
+    if (my_part == nullptr) return;
     if ((lane & 7) == 0) {
       float* pr = my_part + (4 * warp + (lane >> 3)) * (DV + 2) + DV;
       pr[0] = m_run; pr[1] = l_run;
@@ -324,6 +329,13 @@ attention_shared_key_combine_kernel(const float* __restrict__ part, int splits, 
   }
 }
 
+// Blocks along the heads (grid y) for this shape: a block takes 16 heads, or 32 as two tiles for single tokens.
+extern "C" int rl_attention_shared_key_head_blocks(int num_heads, int key_dim, int one_token_each) {
+  if (num_heads <= 0 || key_dim <= 0) return 0;
+  const int groups = (num_heads + 15) / 16;
+  return one_token_each && groups >= 2 && sk_prompt_tiles(key_dim) == 2 ? (groups + 1) / 2 : groups;
+}
+
 // 1 if the kernel takes this shape: rows of key_dim elements (a multiple of 16) whose first value_dim (a multiple of
 // 8, at most 512) are the value, and a key block pair that fits shared memory.
 extern "C" int rl_attention_shared_key_supported(int num_heads, int key_dim, int value_dim) {
@@ -367,9 +379,11 @@ extern "C" int rl_attention_shared_key(const void* q, int ldq, const void* k_poo
   if (num_seqs == 0 || num_tiles == 0) return RL_OK;
   const int groups = (num_heads + 15) / 16;
   RL_REQUIRE(groups <= 65535, "rl_attention_shared_key: too many heads");
-  const int MT = one_token_each ? 1 : sk_prompt_tiles(key_dim);
+  // single tokens of more than 16 heads: the two tiles of a block are two head groups of the token
+  const int head_tiles = one_token_each && groups >= 2 && sk_prompt_tiles(key_dim) == 2;
+  const int MT = one_token_each && !head_tiles ? 1 : sk_prompt_tiles(key_dim);
   const SkLayout L = sk_layout(key_dim, MT);
-  const dim3 grid(num_tiles, groups, splits), block(MT * SK_WARPS * 32);
+  const dim3 grid(num_tiles, head_tiles ? (groups + 1) / 2 : groups, splits), block(MT * SK_WARPS * 32);
   const float sl2 = scale * 1.4426950408889634f;
 #define RL_SK_LAUNCH(NTW)                                                                                                   \
   do {                                                                                                                      \
@@ -389,7 +403,7 @@ extern "C" int rl_attention_shared_key(const void* q, int ldq, const void* k_poo
     attention_shared_key_kernel<NTW, MTV><<<grid, block, L.bytes, stream>>>(                                                     \
         (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, page_table, max_pages, cu_seqlens, seq_slots, kv_lens,  \
         num_seqs, one_token_each, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)gate, ldg, num_heads, key_dim, value_dim, \
-        sl2, window, splits, part);                                                                                         \
+        sl2, window, splits, part, head_tiles);                                                                             \
   } while (0)
   if (value_dim <= 64) RL_SK_LAUNCH(2);
   else if (value_dim <= 128) RL_SK_LAUNCH(4);

@@ -59,6 +59,7 @@ _SIGNATURES = {
                                 _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p,
                                 _c_void_p],
     "rl_attention_shared_key_block_tokens": [_c_int, _c_int, _c_int],
+    "rl_attention_shared_key_head_blocks": [_c_int, _c_int, _c_int],
     "rl_heads_linear": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "rl_embedding_pair": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll,
                           _c_float, _c_ll, _c_ll, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
@@ -1336,7 +1337,8 @@ def attention_shared_key(q: torch.Tensor, k_pool: torch.Tensor, page_table: torc
     groups = -(-num_heads // 16)
     splits, part = 1, None
     if one_each:
-        splits = max(1, min(8, num_sms() // (B * groups)))
+        along_heads = int(library().rl_attention_shared_key_head_blocks(num_heads, key_dim, 1))
+        splits = max(1, min(8, num_sms() // (B * along_heads)))
         if window:
             splits = min(splits, -(-int(window) // PAGE_SIZE) + 1)
         if splits > 1:
