@@ -276,6 +276,58 @@ latent_prepare_kernel(const T* __restrict__ u, int ldu, int q_rank, int kv_rank,
   for (int i = threadIdx.x; i < rd; i += HP_THREADS) rl_st(dst + kv_rank + i, hp_turned(c + kv_rank, i, rot, interleaved, pos, inv_freq));
 }
 
+// The same with a thread owning neighbouring pairs (all widths, strides and offsets even; rotation of neighbours
+// or none): accesses of twice the width, one sine and cosine a pair.
+template <typename T>
+__global__ void __launch_bounds__(HP_THREADS)
+latent_prepare_pairs_kernel(const T* __restrict__ u, int ldu, int q_rank, int kv_rank, int rd, const float* __restrict__ q_w,
+                            const float* __restrict__ kv_w, float eps, T* __restrict__ cq, int ldc, const int* __restrict__ positions,
+                            const int* __restrict__ slot_of_token, const int* __restrict__ page_table, int max_pages,
+                            const float* __restrict__ inv_freq, int rot, T* __restrict__ k_pool) {
+  __shared__ float s_part[HP_THREADS / 32];
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  const int m = blockIdx.x;
+  const T* row = u + (size_t)m * ldu;
+  const int pos = positions[m];
+  if (q_rank > 0) {
+    float ss = 0.f;
+    for (int i = 2 * threadIdx.x; i < q_rank; i += 2 * HP_THREADS) {
+      const float2 v = hp_ld2(row + i);
+      ss = fmaf(v.y, v.y, fmaf(v.x, v.x, ss));
+    }
+    const float r = 1.0f / sqrtf(hp_block_sum(ss, s_part) / (float)q_rank + eps);
+    for (int i = 2 * threadIdx.x; i < q_rank; i += 2 * HP_THREADS) {
+      const float2 v = hp_ld2(row + i);
+      hp_st2(cq + (size_t)m * ldc + i, v.x * r * q_w[i], v.y * r * q_w[i + 1]);
+    }
+  }
+  const T* c = row + q_rank;
+  float ss = 0.f;
+  for (int i = 2 * threadIdx.x; i < kv_rank; i += 2 * HP_THREADS) {
+    const float2 v = hp_ld2(c + i);
+    ss = fmaf(v.y, v.y, fmaf(v.x, v.x, ss));
+  }
+  const float r = 1.0f / sqrtf(hp_block_sum(ss, s_part) / (float)kv_rank + eps);
+  if (k_pool == nullptr) return;
+  const int slot = slot_of_token[m];
+  const int page = page_table[(size_t)slot * max_pages + pos / RL_PAGE];
+  T* dst = k_pool + ((size_t)page * RL_PAGE + pos % RL_PAGE) * (kv_rank + rd);
+  for (int i = 2 * threadIdx.x; i < kv_rank; i += 2 * HP_THREADS) {
+    const float2 v = hp_ld2(c + i);
+    hp_st2(dst + i, v.x * r * kv_w[i], v.y * r * kv_w[i + 1]);
+  }
+  for (int i = 2 * threadIdx.x; i < rd; i += 2 * HP_THREADS) {
+    float2 v = hp_ld2(c + kv_rank + i);
+    if (i < rot) {
+      float sn, cs;
+      sincosf((float)pos * inv_freq[i >> 1], &sn, &cs);
+      v = make_float2(v.x * cs - v.y * sn, v.y * cs + v.x * sn);
+    }
+    hp_st2(dst + kv_rank + i, v.x, v.y);
+  }
+}
+
 // u [M, ldu] with columns [0, q_rank) | [q_rank, q_rank + kv_rank) | [.., + rd); q_w float [q_rank], kv_w float [kv_rank];
 // cq [M, ldc]; k_pool [pages, 1, RL_PAGE, kv_rank + rd] (null: nothing is cached).  q_rank 0: no query latent.
 extern "C" int rl_latent_prepare(const void* u, int ldu, int dtype, int q_rank, int kv_rank, int rot_dim, const float* q_w,
@@ -288,7 +340,17 @@ extern "C" int rl_latent_prepare(const void* u, int ldu, int dtype, int q_rank, 
   RL_REQUIRE(ldu >= q_rank + kv_rank + rot_dim && (q_rank == 0 || ldc >= q_rank), "rl_latent_prepare: row strides too small");
   RL_REQUIRE(kv_w != nullptr && (q_rank == 0 || (q_w != nullptr && cq != nullptr)), "rl_latent_prepare: a norm weight or the output is missing");
   if (num_tokens == 0) return RL_OK;
-  if (dtype == RL_F32)
+  const uintptr_t two = dtype == RL_F32 ? 8 : 4;
+  const bool pairs = (interleaved || rotary_dim == 0) && q_rank % 2 == 0 && kv_rank % 2 == 0 && rot_dim % 2 == 0 && ldu % 2 == 0 &&
+                     ldc % 2 == 0 && (uintptr_t)u % two == 0 && (uintptr_t)cq % two == 0 && (uintptr_t)k_pool % two == 0;
+  if (pairs && dtype == RL_F32)
+    rl_launch_pdl(latent_prepare_pairs_kernel<float>, num_tokens, HP_THREADS, 0, stream, (const float*)u, ldu, q_rank, kv_rank, rot_dim,
+                  q_w, kv_w, eps, (float*)cq, ldc, positions, slot_of_token, page_table, max_pages, inv_freq, rotary_dim, (float*)k_pool);
+  else if (pairs && dtype == RL_BF16)
+    rl_launch_pdl(latent_prepare_pairs_kernel<__nv_bfloat16>, num_tokens, HP_THREADS, 0, stream, (const __nv_bfloat16*)u, ldu, q_rank,
+                  kv_rank, rot_dim, q_w, kv_w, eps, (__nv_bfloat16*)cq, ldc, positions, slot_of_token, page_table, max_pages, inv_freq,
+                  rotary_dim, (__nv_bfloat16*)k_pool);
+  else if (dtype == RL_F32)
     rl_launch_pdl(latent_prepare_kernel<float>, num_tokens, HP_THREADS, 0, stream, (const float*)u, ldu, q_rank, kv_rank, rot_dim, q_w,
                   kv_w, eps, (float*)cq, ldc, positions, slot_of_token, page_table, max_pages, inv_freq, rotary_dim, interleaved,
                   (float*)k_pool);
@@ -317,6 +379,27 @@ latent_query_kernel(const T* __restrict__ q, int ldq, int H, int hd, int rd, con
   }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(HP_THREADS)
+latent_query_pairs_kernel(const T* __restrict__ q, int ldq, int H, int hd, int rd, const int* __restrict__ positions,
+                          const float* __restrict__ inv_freq, int rot, T* __restrict__ out, int ldo, int lat) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  const int m = blockIdx.x;
+  const int pos = positions[m];
+  const int half = rd >> 1;
+  for (int e = threadIdx.x; e < H * half; e += HP_THREADS) {
+    const int h = e / half, i = 2 * (e % half);
+    float2 v = hp_ld2(q + (size_t)m * ldq + (size_t)h * (hd + rd) + hd + i);
+    if (i < rot) {
+      float sn, cs;
+      sincosf((float)pos * inv_freq[i >> 1], &sn, &cs);
+      v = make_float2(v.x * cs - v.y * sn, v.y * cs + v.x * sn);
+    }
+    hp_st2(out + (size_t)m * ldo + (size_t)h * (lat + rd) + lat + i, v.x, v.y);
+  }
+}
+
 // q [M, ldq]: H heads of [hd | rd]; out [M, ldo]: H heads of [lat | rd], of which this fills the rd columns.
 extern "C" int rl_latent_query(const void* q, int ldq, int dtype, int num_heads, int head_dim, int rot_dim, const int* positions,
                                const float* inv_freq, int rotary_dim, int interleaved, void* out, int ldo, int latent_dim,
@@ -326,7 +409,16 @@ extern "C" int rl_latent_query(const void* q, int ldq, int dtype, int num_heads,
              rotary_dim, rot_dim);
   RL_REQUIRE(ldq >= num_heads * (head_dim + rot_dim) && ldo >= num_heads * (latent_dim + rot_dim), "rl_latent_query: row strides too small");
   if (num_tokens == 0 || rot_dim == 0) return RL_OK;
-  if (dtype == RL_F32)
+  const uintptr_t two = dtype == RL_F32 ? 8 : 4;
+  const bool pairs = (interleaved || rotary_dim == 0) && head_dim % 2 == 0 && rot_dim % 2 == 0 && latent_dim % 2 == 0 && ldq % 2 == 0 &&
+                     ldo % 2 == 0 && (uintptr_t)q % two == 0 && (uintptr_t)out % two == 0;
+  if (pairs && dtype == RL_F32)
+    rl_launch_pdl(latent_query_pairs_kernel<float>, num_tokens, HP_THREADS, 0, stream, (const float*)q, ldq, num_heads, head_dim, rot_dim,
+                  positions, inv_freq, rotary_dim, (float*)out, ldo, latent_dim);
+  else if (pairs && dtype == RL_BF16)
+    rl_launch_pdl(latent_query_pairs_kernel<__nv_bfloat16>, num_tokens, HP_THREADS, 0, stream, (const __nv_bfloat16*)q, ldq, num_heads,
+                  head_dim, rot_dim, positions, inv_freq, rotary_dim, (__nv_bfloat16*)out, ldo, latent_dim);
+  else if (dtype == RL_F32)
     rl_launch_pdl(latent_query_kernel<float>, num_tokens, HP_THREADS, 0, stream, (const float*)q, ldq, num_heads, head_dim, rot_dim,
                   positions, inv_freq, rotary_dim, interleaved, (float*)out, ldo, latent_dim);
   else if (dtype == RL_BF16)

@@ -190,7 +190,7 @@ def test_rotation_of_neighbours_then_unit_heads_values_from_keys(dtype, H, G, hd
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,hd,rd,r,qr,dims", [(3, 24, 8, 32, 40, 8), (2, 8, 16, 24, 16, 16), (4, 12, 8, 40, 20, 4), (1, 40, 6, 12, 36, 0),
-                                               (2, 32, 0, 64, 24, 0)])
+                                               (2, 32, 0, 64, 24, 0), (3, 9, 4, 15, 11, 4)])
 def test_latents_are_normed_and_the_shared_key_part_turned(dtype, H, hd, rd, r, qr, dims):
     """From one projected row [query latent | key/value latent | rotary key | gates]: both latents normed with their plain
     weights, the rotary key turned, the key row [latent | rotary key] in its page; and the query's rotary part turned
@@ -723,7 +723,7 @@ def test_a_product_a_head_in_one_launch(dtype, M, H, N, K, x_head, out_head):
     assert (got[:, (H - 1) * out_head + N:] == 7.0).all()
 
 
-@pytest.mark.parametrize("H,r,rd", [(16, 64, 32), (4, 96, 16), (3, 32, 16)])
+@pytest.mark.parametrize("H,r,rd", [(16, 64, 32), (4, 96, 16), (3, 32, 16), (32, 64, 32), (40, 32, 16)])
 @pytest.mark.parametrize("window", [None, 130])
 def test_heads_over_one_cached_row_with_unequal_sequences_in_one_step(H, r, rd, window):
     """Five sequences of unequal lengths as one prompt step (blocks of two tiles that end inside a sequence), then four
