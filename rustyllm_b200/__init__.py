@@ -13,7 +13,8 @@ from .config.spec import LayerSpec, ModelSpec, ParamSource, ParamSpec, PartSpec 
 from .engine.generate import GenerationOptions, GenerationResult, GenerationStats  # noqa: F401
 from .engine.runner import LoadInfo, Runner  # noqa: F401
 from .engine.step import Engine  # noqa: F401
-from .models import forilorn as _forilorn  # noqa: F401  (registers the architecture)
+from .models import besuzen as _besuzen  # noqa: F401  (registers the architecture)
+from .models import forilorn as _forilorn  # noqa: F401
 from .models import llama as _llama  # noqa: F401
 from .models import mogutar as _mogutar  # noqa: F401
 from .models import mosurax as _mosurax  # noqa: F401

@@ -111,12 +111,12 @@ def inspect(model_dir: str, list_tensors: bool) -> int:
     from .weights.safetensors_io import Checkpoint
     cfg = read_config_json(model_dir)
     arch = resolve_architecture(cfg)
-    typed = arch.parse_config(cfg)
+    ck = Checkpoint(model_dir)
+    typed = arch.parse_for(cfg, {n: tuple(e.shape) for n, e in ck.entries.items()})
     spec = arch.build_spec(typed)
     print(f"architecture: {arch.name}")
     for k, v in (typed.to_dict() if hasattr(typed, "to_dict") else dict(typed)).items():
         print(f"  {k}: {v}")
-    ck = Checkpoint(model_dir)
     print(f"checkpoint: {len(ck.entries)} tensors in {len(ck.files)} file(s), {ck.total_bytes} bytes")
     if list_tensors:
         for name, e in sorted(ck.entries.items()):

@@ -7,7 +7,7 @@ name is an error that lists the known ones (src/runtime.rs:1236-1245).
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Mapping, Sequence
+from typing import Any, Callable, Dict, Mapping, Optional, Sequence
 
 from .spec import ModelSpec
 
@@ -21,15 +21,26 @@ class Architecture:
     name: str
     parse_config: Callable[[Mapping[str, Any]], Any]   # config.json dict -> typed config
     build_spec: Callable[[Any], ModelSpec]             # typed config -> ModelSpec
+    # (typed config, {tensor name: shape} of the checkpoint) -> typed config with the sizes filled in that no key of
+    # config.json holds; None: the configuration is complete as parsed
+    sizes_from_checkpoint: Optional[Callable[[Any, Mapping[str, tuple]], Any]] = None
+
+    def parse_for(self, config_dict: Mapping[str, Any], shapes: Optional[Mapping[str, tuple]] = None) -> Any:
+        """The typed configuration of a model folder: config.json, completed from the checkpoint's tensor shapes
+        where the design leaves a size to them."""
+        cfg = self.parse_config(config_dict)
+        if shapes is not None and self.sizes_from_checkpoint is not None:
+            cfg = self.sizes_from_checkpoint(cfg, shapes)
+        return cfg
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 
 
-def register_architecture(names: Sequence[str], parse_config, build_spec) -> Architecture:
+def register_architecture(names: Sequence[str], parse_config, build_spec, sizes_from_checkpoint=None) -> Architecture:
     """Register one architecture under every name config.json may carry for it
     (an entry of ``architectures`` or the ``model_type``)."""
-    arch = Architecture(name=names[0], parse_config=parse_config, build_spec=build_spec)
+    arch = Architecture(name=names[0], parse_config=parse_config, build_spec=build_spec, sizes_from_checkpoint=sizes_from_checkpoint)
     for n in names:
         _ARCHITECTURES[n] = arch
     return arch

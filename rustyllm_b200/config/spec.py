@@ -59,6 +59,8 @@ class ParamSpec:
     @property
     def shape(self) -> Tuple[int, ...]:
         first = self.sources[0].shape
+        if len(first) == 0:            # a scalar: one source, taken as it is
+            return ()
         rows = sum(s.shape[0] for s in self.sources)
         return (rows,) + tuple(first[1:])
 

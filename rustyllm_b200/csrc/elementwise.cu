@@ -499,3 +499,37 @@ extern "C" int rl_sigmoid_gate(void* y, int ldy, const void* g, int ldg, int dty
   RL_LAUNCH_CHECK("rl_sigmoid_gate");
   return RL_OK;
 }
+
+// ------------------------------------------------------------------ gated feed-forward with the tanh form of gelu
+// out = gelu_tanh(gate) * up, for products that did not carry the activation in their epilogue (the 32-bit path,
+// shapes the tensor-core product cannot address).  Layouts as for rl_swiglu.
+template <typename T>
+__global__ void geglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int M, int I, int interleaved) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)M * I) return;
+  const size_t m = idx / I, i = idx % I;
+  const T* row = gu + m * 2 * (size_t)I;
+  const float g = rl_ld(interleaved ? row + 2 * i : row + i);
+  const float u = rl_ld(interleaved ? row + 2 * i + 1 : row + I + i);
+  const float act = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  rl_st(out + idx, act * u);
+}
+
+extern "C" int rl_geglu(const void* gate_up, void* out, int dtype, int num_tokens, int intermediate, int interleaved,
+                        cudaStream_t stream) {
+  RL_REQUIRE(num_tokens >= 0 && intermediate > 0, "rl_geglu: bad sizes M=%d I=%d", num_tokens, intermediate);
+  if (num_tokens == 0) return RL_OK;
+  const size_t total = (size_t)num_tokens * intermediate;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == RL_F32)
+    rl_launch_pdl(geglu_kernel<float>, blocks, 256, 0, stream, (const float*)gate_up, (float*)out, num_tokens, intermediate, interleaved);
+  else if (dtype == RL_BF16)
+    rl_launch_pdl(geglu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, num_tokens,
+                  intermediate, interleaved);
+  else
+    RL_REQUIRE(false, "rl_geglu: unknown dtype %d", dtype);
+  RL_LAUNCH_CHECK("rl_geglu");
+  return RL_OK;
+}

@@ -119,7 +119,7 @@ __device__ __forceinline__ void tile_epilogue(uint32_t tmem_acc, int quarter, in
 #pragma unroll
       for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rs[c * 16 + j]);
     }
-    if (out_mode == TC_OUT_SWIGLU) {
+    if (tc_out_gated(out_mode)) {
       // weight rows are (gate_0, up_0, gate_1, up_1, ...): the even lane holds the gate, its
       // odd neighbour the up value of the same output column n / 2
       // ... the even lane finishes columns 0-7 of the chunk, the odd lane columns 8-15: each
@@ -132,7 +132,7 @@ __device__ __forceinline__ void tile_epilogue(uint32_t tmem_acc, int quarter, in
         const float got = __shfl_xor_sync(0xffffffffu, even ? hi : lo, 1);
         const float gate = even ? lo : got, up = even ? got : hi;
         const int m = m0 + c * 16 + (even ? j : j + 8);
-        if ((n | 1) < N && m < M) ob[(size_t)m * ldo + (n >> 1)] = __float2bfloat16_rn(silu_mul(gate, up));
+        if ((n | 1) < N && m < M) ob[(size_t)m * ldo + (n >> 1)] = __float2bfloat16_rn(gated_mul(gate, up, out_mode));
       }
     } else if (out_mode == TC_OUT_ADD_F32) {
       // all sixteen loads of the residual first, then the stores: a load placed after
@@ -787,9 +787,9 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
   const float* norm_weight = fuse.norm_weight;
   RL_REQUIRE(rl_gemm_tc_supported(A, W, M, N, K, lda), "rl_gemm_tc: operands not supported (M=%d N=%d K=%d lda=%d; K and lda "
              "must be multiples of 8 and the bases 16-byte aligned)", M, N, K, lda);
-  RL_REQUIRE(out_mode >= 0 && out_mode <= 5, "rl_gemm_tc: unknown output mode %d", out_mode);
-  RL_REQUIRE(out_mode != TC_OUT_SWIGLU || N % 2 == 0, "rl_gemm_tc: the SwiGLU epilogue needs an even number of weight rows, got %d", N);
-  RL_REQUIRE(ldo >= (out_mode == TC_OUT_SWIGLU ? N / 2 : N) && err != nullptr, "rl_gemm_tc: bad output stride or null error word");
+  RL_REQUIRE(out_mode >= 0 && out_mode <= 6, "rl_gemm_tc: unknown output mode %d", out_mode);
+  RL_REQUIRE(!tc_out_gated(out_mode) || N % 2 == 0, "rl_gemm_tc: the SwiGLU epilogue needs an even number of weight rows, got %d", N);
+  RL_REQUIRE(ldo >= (tc_out_gated(out_mode) ? N / 2 : N) && err != nullptr, "rl_gemm_tc: bad output stride or null error word");
   RL_REQUIRE(force_splits >= 0 && force_splits <= 8, "rl_gemm_tc: the number of K parts must be 1 to 8 (0: chosen from the shapes), got %d", force_splits);
   RL_REQUIRE(scale_partials == nullptr || fuse.scale_count > 0, "rl_gemm_tc: row scales without their sums");
   RL_REQUIRE(norm_weight == nullptr || (out_mode == TC_OUT_ADD_F32 && fuse.norm_out != nullptr && fuse.norm_partials != nullptr && fuse.ld_norm >= N),

@@ -6,6 +6,10 @@
 // mode 0: a_t = decay[h], b_t = 1 (linear attention with a fixed decay a head);
 // mode 1: dt = softplus(dt_raw[t, h] + dt_bias[h]), a_t = exp(-exp(rate[h]) dt), b_t = dt (a selective
 //         state space: q = C, k = B, v = x, skip = D).
+// mode 2: a decay a key channel and token, and a bonus for the current token that does not enter the state:
+//           o_t = (S_{t-1} + diag(u_h) k_t v_t^T)^T q_t,   S_t = diag(w_t) S_{t-1} + k_t v_t^T,
+//         w_t = exp(-exp(wlog[t, h, :])) from the float logarithms `wlog` (the decay is never stored in fewer bits),
+//         u float [H, dk].  (Template parameter CH; the other two modes are CH = false.)
 // Query and key heads may be shared by `hpg` consecutive heads (head h reads group h / hpg).  With act = 1
 // q, k and v pass through silu as they are loaded.  Everything behind the loads is 32-bit.
 //
@@ -28,13 +32,14 @@
 __device__ __forceinline__ float scan_silu(float z, float) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float scan_silu(float z, __nv_bfloat16) { return __fdividef(z, 1.0f + __expf(-z)); }
 
-template <typename T, int NPT, int R, int SCAN_COLS, int SCAN_TILE>
+template <typename T, int NPT, int R, int SCAN_COLS, int SCAN_TILE, bool CH>
 __global__ void __launch_bounds__(R * SCAN_COLS)
 linear_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int ldk, const T* __restrict__ v, int ldv,
                    const T* __restrict__ dt_raw, int lddt, const float* __restrict__ dt_bias, const float* __restrict__ rate,
                    const float* __restrict__ skip, int mode, int act, const int* __restrict__ cu_seqlens,
                    const int* __restrict__ seq_slots, float* __restrict__ state, long long state_stride,
-                   float* __restrict__ out, int ldo, int H, int hpg, int dk, int dv) {
+                   float* __restrict__ out, int ldo, int H, int hpg, int dk, int dv, const float* __restrict__ wlog, int ldw,
+                   const float* __restrict__ bonus) {
   constexpr int DKP = NPT * R;                  // dk rounded up to what the lanes of a column hold: a power of two
   constexpr int THREADS = R * SCAN_COLS;
   // Two shapes.  Many tokens a sequence (NPT <= 8): a lane holds NPT consecutive rows (16-byte loads from shared
@@ -46,6 +51,7 @@ linear_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, in
   // rows beyond dk are staged as zeros, so the walk needs no bounds: their state stays zero
   __shared__ __align__(16) float s_q[SCAN_TILE][DKP], s_k[SCAN_TILE][DKP];
   __shared__ float s_v[SCAN_TILE][SCAN_COLS], s_bv[SCAN_TILE][SCAN_COLS], s_a[SCAN_TILE];
+  __shared__ __align__(16) float s_w[CH ? SCAN_TILE : 1][CH ? DKP : 4];      // the tokens' decays a key channel
   rl_pdl_trigger();
   rl_pdl_wait();
   const int b = blockIdx.x, h = blockIdx.y;
@@ -55,20 +61,24 @@ linear_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, in
   const int lo = cu_seqlens[b], hi = cu_seqlens[b + 1];
   auto row_of = [&](int i) { return LONG ? NPT * r + i : r + R * i; };
   float* st = state + (size_t)seq_slots[b] * state_stride + ((size_t)h * dv + (live ? col : 0)) * dk;
-  float S[NPT];
+  float S[NPT], U[CH ? NPT : 1];
 #pragma unroll
   for (int i = 0; i < NPT; ++i) S[i] = (live && row_of(i) < dk) ? st[row_of(i)] : 0.f;
+  if constexpr (CH) {
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) U[i] = row_of(i) < dk ? bonus[(size_t)h * dk + row_of(i)] : 0.f;
+  }
   const int qk0 = (h / hpg) * dk;
   const float skip_h = skip ? skip[h] : 0.f;
-  const float rate_h = rate[h], bias_h = mode ? dt_bias[h] : 0.f;
-  const float neg_rate = mode ? -expf(rate_h) : 0.f;
+  const float rate_h = CH ? 0.f : rate[h], bias_h = (!CH && mode) ? dt_bias[h] : 0.f;
+  const float neg_rate = (!CH && mode) ? -expf(rate_h) : 0.f;
 
   // what a thread stages of a tile: QI elements of q and of k (element idx = tid + j * THREADS of the tile's
   // [SCAN_TILE, DKP]), one of v (threads below SCAN_TILE * SCAN_COLS) with its token's raw step size
   constexpr int VT = SCAN_TILE * SCAN_COLS;
   constexpr int QI = LONG ? SCAN_TILE * DKP / THREADS : 1;
   static_assert(!LONG || QI * THREADS == SCAN_TILE * DKP, "a tile's q and k are dealt evenly to the threads");
-  float fq[QI], fk[QI], fv = 0.f, fdt = 0.f;
+  float fq[QI], fk[QI], fw[CH ? QI : 1], fv = 0.f, fdt = 0.f;
   auto fetch = [&](int t0, int nt) {            // raw values of the tile at t0 into registers (zeros outside)
 #pragma unroll
     for (int j = 0; j < QI; ++j) {
@@ -76,11 +86,12 @@ linear_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, in
       const bool in = tt < nt && n < dk;
       fq[j] = in ? rl_ld(q + (size_t)(t0 + tt) * ldq + qk0 + n) : 0.f;
       fk[j] = in ? rl_ld(k + (size_t)(t0 + tt) * ldk + qk0 + n) : 0.f;
+      if constexpr (CH) fw[j] = in ? wlog[(size_t)(t0 + tt) * ldw + (size_t)h * dk + n] : 0.f;
     }
     if (THREADS >= VT ? tid < VT : true) {
       const int tt = tid / SCAN_COLS, cc = blockIdx.z * SCAN_COLS + tid % SCAN_COLS;
       fv = (tt < nt && cc < dv) ? rl_ld(v + (size_t)(t0 + tt) * ldv + (size_t)h * dv + cc) : 0.f;
-      fdt = (mode && tt < nt) ? rl_ld(dt_raw + (size_t)(t0 + tt) * lddt + h) : 0.f;
+      fdt = (!CH && mode && tt < nt) ? rl_ld(dt_raw + (size_t)(t0 + tt) * lddt + h) : 0.f;
     }
   };
   auto step_size = [&](float raw) { const float z = raw + bias_h; return z > 20.0f ? z : log1pf(expf(z)); };
@@ -92,14 +103,15 @@ linear_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, in
       if (act && n < dk) { qv = scan_silu(qv, T()); kv = scan_silu(kv, T()); }
       s_q[tt][n] = qv;
       s_k[tt][n] = kv;
+      if constexpr (CH) s_w[tt][n] = n < dk ? expf(-expf(fw[j])) : 0.f;
     }
     if (tid < VT) {
       const int tt = tid / SCAN_COLS;
       const float vv = act ? scan_silu(fv, T()) : fv;
-      const float dt = mode ? step_size(fdt) : 1.0f;
+      const float dt = (!CH && mode) ? step_size(fdt) : 1.0f;
       s_v[tt][tid % SCAN_COLS] = vv;
       s_bv[tt][tid % SCAN_COLS] = dt * vv;
-      if (tid % SCAN_COLS == 0) s_a[tt] = mode ? expf(neg_rate * dt) : rate_h;
+      if (tid % SCAN_COLS == 0) s_a[tt] = (!CH && mode) ? expf(neg_rate * dt) : rate_h;
     }
   };
   if (LONG && lo < hi) fetch(lo, min(SCAN_TILE, hi - lo));
@@ -120,15 +132,16 @@ linear_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, in
         }
         s_q[tt][n] = qv;
         s_k[tt][n] = kv;
+        if constexpr (CH) s_w[tt][n] = n < dk ? expf(-expf(wlog[(size_t)(t0 + tt) * ldw + (size_t)h * dk + n])) : 0.f;
       }
       for (int idx = tid; idx < nt * SCAN_COLS; idx += THREADS) {
         const int tt = idx / SCAN_COLS, cc = blockIdx.z * SCAN_COLS + idx % SCAN_COLS;
         float vv = cc < dv ? rl_ld(v + (size_t)(t0 + tt) * ldv + (size_t)h * dv + cc) : 0.f;
         if (act) vv = scan_silu(vv, T());
-        const float dt = mode ? step_size(rl_ld(dt_raw + (size_t)(t0 + tt) * lddt + h)) : 1.0f;
+        const float dt = (!CH && mode) ? step_size(rl_ld(dt_raw + (size_t)(t0 + tt) * lddt + h)) : 1.0f;
         s_v[tt][idx % SCAN_COLS] = vv;
         s_bv[tt][idx % SCAN_COLS] = dt * vv;
-        if (idx % SCAN_COLS == 0) s_a[tt] = mode ? expf(neg_rate * dt) : rate_h;
+        if (idx % SCAN_COLS == 0) s_a[tt] = (!CH && mode) ? expf(neg_rate * dt) : rate_h;
       }
     }
     __syncthreads();
@@ -147,6 +160,20 @@ linear_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, in
 #pragma unroll
           for (int i = 0; i < NPT / 4; ++i) {
             const float4 kk = k4[i], qq = q4[i];
+            if constexpr (CH) {
+              // the output reads the state before this token enters it, plus the bonus on the token's own product
+              const float4 ww = reinterpret_cast<const float4*>(&s_w[tt][NPT * r])[i];
+              const float p0 = bv * kk.x, p1 = bv * kk.y, p2 = bv * kk.z, p3 = bv * kk.w;
+              part[tt] = fmaf(fmaf(U[4 * i], p0, S[4 * i]), qq.x, part[tt]);
+              part[tt] = fmaf(fmaf(U[4 * i + 1], p1, S[4 * i + 1]), qq.y, part[tt]);
+              part[tt] = fmaf(fmaf(U[4 * i + 2], p2, S[4 * i + 2]), qq.z, part[tt]);
+              part[tt] = fmaf(fmaf(U[4 * i + 3], p3, S[4 * i + 3]), qq.w, part[tt]);
+              S[4 * i] = fmaf(ww.x, S[4 * i], p0);
+              S[4 * i + 1] = fmaf(ww.y, S[4 * i + 1], p1);
+              S[4 * i + 2] = fmaf(ww.z, S[4 * i + 2], p2);
+              S[4 * i + 3] = fmaf(ww.w, S[4 * i + 3], p3);
+              continue;
+            }
             S[4 * i] = fmaf(a, S[4 * i], bv * kk.x);
             S[4 * i + 1] = fmaf(a, S[4 * i + 1], bv * kk.y);
             S[4 * i + 2] = fmaf(a, S[4 * i + 2], bv * kk.z);
@@ -159,6 +186,12 @@ linear_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, in
         } else {
 #pragma unroll
           for (int i = 0; i < NPT; ++i) {
+            if constexpr (CH) {
+              const float p = bv * s_k[tt][r + R * i];
+              part[tt] = fmaf(fmaf(U[i], p, S[i]), s_q[tt][r + R * i], part[tt]);
+              S[i] = fmaf(s_w[tt][r + R * i], S[i], p);
+              continue;
+            }
             S[i] = fmaf(a, S[i], bv * s_k[tt][r + R * i]);
             part[tt] = fmaf(S[i], s_q[tt][r + R * i], part[tt]);
           }
@@ -182,15 +215,16 @@ linear_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, in
   }
 }
 
-template <typename T>
+template <typename T, bool CH = false>
 static int scan_launch(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const void* dt_raw, int lddt,
                        const float* dt_bias, const float* rate, const float* skip, int mode, int act, const int* cu_seqlens,
                        const int* seq_slots, int num_seqs, float* state, long long state_stride, float* out, int ldo, int H,
-                       int hpg, int dk, int dv, int wide, cudaStream_t stream) {
+                        int hpg, int dk, int dv, int wide, cudaStream_t stream, const float* wlog = nullptr, int ldw = 0,
+                       const float* bonus = nullptr) {
 #define SCAN_GO(NPT, R, COLS)                                                                                                      \
-  rl_launch_pdl(linear_scan_kernel<T, NPT, R, COLS, (NPT > 8 ? 8 : 16)>, dim3(num_seqs, H, (dv + COLS - 1) / COLS), R * COLS, 0, stream, (const T*)q, ldq, \
+  rl_launch_pdl(linear_scan_kernel<T, NPT, R, COLS, (NPT > 8 || (CH && NPT * R > 128) ? 8 : 16), CH>, dim3(num_seqs, H, (dv + COLS - 1) / COLS), R * COLS, 0, stream, (const T*)q, ldq, \
                 (const T*)k, ldk, (const T*)v, ldv, (const T*)dt_raw, lddt, dt_bias, rate, skip, mode, act, cu_seqlens, seq_slots,      \
-                state, state_stride, out, ldo, H, hpg, dk, dv)
+                state, state_stride, out, ldo, H, hpg, dk, dv, wlog, ldw, bonus)
   // tokens a tile: 8 in the shape for single-token steps (64 registers a thread and half the shared memory: 35.7
   // against 39.7 us at 64 sequences), 16 in long steps (8: 759 against 575 us, a barrier pair every 8 tokens)
   // columns of the state a block: 16 in single-token steps (fewer, larger blocks: 0.52 against 0.43 of the copy
@@ -231,5 +265,29 @@ extern "C" int rl_linear_scan(const void* q, int ldq, const void* k, int ldk, co
   else
     RL_REQUIRE(false, "rl_linear_scan: unknown dtype %d", dtype);
   RL_LAUNCH_CHECK("rl_linear_scan");
+  return RL_OK;
+}
+
+// The recurrence with a decay a key channel and a bonus for the current token (mode 2 above).  q, k [M, ld] with
+// head h at columns [h * dk, (h + 1) * dk); v [M, ldv] with head h at [h * dv, (h + 1) * dv); wlog float [M, ldw]
+// with head h at [h * dk, (h + 1) * dk): the decay of key channel n at token t is exp(-exp(wlog[t, h * dk + n]));
+// bonus float [H, dk].  State, output and `wide` as in rl_linear_scan.
+extern "C" int rl_channel_decay_scan(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, int dtype,
+                                     const float* wlog, int ldw, const float* bonus, const int* cu_seqlens, const int* seq_slots,
+                                     int num_seqs, float* state, long long state_stride, float* out, int ldo, int num_heads, int dk,
+                                     int dv, int wide, cudaStream_t stream) {
+  RL_REQUIRE(num_seqs >= 0 && num_heads > 0 && num_heads <= 65535, "rl_channel_decay_scan: bad sizes");
+  RL_REQUIRE(dk > 0 && dk <= SCAN_MAX_DK && dv > 0, "rl_channel_decay_scan: dk %d outside (0, %d] or dv %d", dk, SCAN_MAX_DK, dv);
+  RL_REQUIRE(wlog != nullptr && bonus != nullptr && state != nullptr && ldw >= num_heads * dk, "rl_channel_decay_scan: no decays, bonus or state");
+  if (num_seqs == 0) return RL_OK;
+  if (dtype == RL_F32)
+    scan_launch<float, true>(q, ldq, k, ldk, v, ldv, nullptr, 0, nullptr, nullptr, nullptr, 0, 0, cu_seqlens, seq_slots, num_seqs, state,
+                             state_stride, out, ldo, num_heads, 1, dk, dv, wide, stream, wlog, ldw, bonus);
+  else if (dtype == RL_BF16)
+    scan_launch<__nv_bfloat16, true>(q, ldq, k, ldk, v, ldv, nullptr, 0, nullptr, nullptr, nullptr, 0, 0, cu_seqlens, seq_slots, num_seqs,
+                                     state, state_stride, out, ldo, num_heads, 1, dk, dv, wide, stream, wlog, ldw, bonus);
+  else
+    RL_REQUIRE(false, "rl_channel_decay_scan: unknown dtype %d", dtype);
+  RL_LAUNCH_CHECK("rl_channel_decay_scan");
   return RL_OK;
 }

@@ -180,13 +180,34 @@ extern "C" int rl_moe_route(const void* x, int ldx, const void* router, const fl
 // largest choice scores (of its one, in groups of one); only experts of the `keep` best groups can be chosen.
 // Ties go to the lower index.  One warp: s_score [E] holds the logits on entry, s_choice [E] and s_group
 // [2 * groups] are scratch.
+// Variants, each an argument: `softmax_all` - the scores are the softmax of the logits over all experts instead of
+// their sigmoids; `group_top` - a group's score is the sum of its `group_top` largest choice scores (2 above; 1: its
+// largest); `renorm` - the weights are the chosen scores divided by their sum (+ 1e-20).
 __device__ __forceinline__ void moe_pick_sigmoid(float* s_score, float* s_choice, float* s_group, const float* __restrict__ correction,
                                                  int E, int top, int groups, int keep, int lane, int* __restrict__ ids,
-                                                 float* __restrict__ weights) {
-  for (int e = lane; e < E; e += 32) {
-    const float sc = 1.0f / (1.0f + expf(-s_score[e]));
-    s_score[e] = sc;
-    s_choice[e] = sc + (correction ? correction[e] : 0.f);
+                                                 float* __restrict__ weights, int softmax_all = 0, int group_top = 2, int renorm = 0) {
+  if (softmax_all) {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s_score[e]);
+    mx = rl_warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      const float p = expf(s_score[e] - mx);
+      s_score[e] = p;
+      sum += p;
+    }
+    sum = rl_warp_sum(sum);
+    for (int e = lane; e < E; e += 32) {
+      const float sc = s_score[e] / sum;
+      s_score[e] = sc;
+      s_choice[e] = sc + (correction ? correction[e] : 0.f);
+    }
+  } else {
+    for (int e = lane; e < E; e += 32) {
+      const float sc = 1.0f / (1.0f + expf(-s_score[e]));
+      s_score[e] = sc;
+      s_choice[e] = sc + (correction ? correction[e] : 0.f);
+    }
   }
   __syncwarp();
   if (groups > 1 && keep < groups) {
@@ -198,7 +219,7 @@ __device__ __forceinline__ void moe_pick_sigmoid(float* s_score, float* s_choice
         if (v > t1) { t2 = t1; t1 = v; }
         else if (v > t2) t2 = v;
       }
-      s_group[g] = size > 1 ? t1 + t2 : t1;
+      s_group[g] = (size > 1 && group_top > 1) ? t1 + t2 : t1;
       s_group[groups + g] = 0.f;           // 1: the group is kept
     }
     __syncwarp();
@@ -244,6 +265,10 @@ __device__ __forceinline__ void moe_pick_sigmoid(float* s_score, float* s_choice
     if (lane == 0) s_choice[at] = -INFINITY;
     __syncwarp();
   }
+  if (renorm) {
+    const float total = rl_warp_sum(lane < top ? chosen_w : 0.f);
+    chosen_w = chosen_w / (total + 1e-20f);
+  }
   if (lane < top) {
     ids[lane] = chosen_id;
     weights[lane] = chosen_w;
@@ -253,7 +278,8 @@ __device__ __forceinline__ void moe_pick_sigmoid(float* s_score, float* s_choice
 template <typename T>
 __global__ void __launch_bounds__(MOE_THREADS)
 moe_route_sigmoid_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ wr, const float* __restrict__ correction,
-                         int d, int E, int top, int groups, int keep, int* __restrict__ ids, float* __restrict__ weights) {
+                         int d, int E, int top, int groups, int keep, int* __restrict__ ids, float* __restrict__ weights, int softmax_all,
+                         int group_top, int renorm) {
   extern __shared__ float s_logit[];     // scores [E], choice scores [E], groups [2 * groups], then the token's input [d]
   const int Ep = (E + 3) & ~3;
   float* s_x = s_logit + 4 * Ep;
@@ -262,13 +288,14 @@ moe_route_sigmoid_kernel(const T* __restrict__ x, int ldx, const T* __restrict__
   moe_logits(x, ldx, wr, (const float*)nullptr, d, E, s_logit, s_x);
   if (threadIdx.x >= 32) return;
   const size_t m = blockIdx.x;
-  moe_pick_sigmoid(s_logit, s_logit + Ep, s_logit + 2 * Ep, correction, E, top, groups, keep, threadIdx.x, ids + m * top, weights + m * top);
+  moe_pick_sigmoid(s_logit, s_logit + Ep, s_logit + 2 * Ep, correction, E, top, groups, keep, threadIdx.x, ids + m * top, weights + m * top,
+                   softmax_all, group_top, renorm);
 }
 
 // from logits a matrix product has made: one warp a token
 __global__ void __launch_bounds__(32)
 moe_select_sigmoid_kernel(const float* __restrict__ logits, int E, int top, const float* __restrict__ correction, int groups, int keep,
-                          int* __restrict__ ids, float* __restrict__ weights) {
+                          int* __restrict__ ids, float* __restrict__ weights, int softmax_all, int group_top, int renorm) {
   extern __shared__ float s_logit[];
   const int Ep = (E + 3) & ~3;
   rl_pdl_trigger();
@@ -276,7 +303,8 @@ moe_select_sigmoid_kernel(const float* __restrict__ logits, int E, int top, cons
   const size_t m = blockIdx.x;
   for (int e = threadIdx.x; e < E; e += 32) s_logit[e] = logits[m * E + e];
   __syncwarp();
-  moe_pick_sigmoid(s_logit, s_logit + Ep, s_logit + 2 * Ep, correction, E, top, groups, keep, threadIdx.x, ids + m * top, weights + m * top);
+  moe_pick_sigmoid(s_logit, s_logit + Ep, s_logit + 2 * Ep, correction, E, top, groups, keep, threadIdx.x, ids + m * top, weights + m * top,
+                   softmax_all, group_top, renorm);
 }
 
 static int moe_sigmoid_args(const char* who, int num_experts, int top, int groups, int keep) {
@@ -288,35 +316,50 @@ static int moe_sigmoid_args(const char* who, int num_experts, int top, int group
   return RL_OK;
 }
 
-extern "C" int rl_moe_select_sigmoid(const float* logits, int num_tokens, int num_experts, int top, const float* correction, int groups,
-                                     int keep, int* ids, float* weights, cudaStream_t stream) {
-  RL_REQUIRE(num_tokens >= 0, "rl_moe_select_sigmoid: bad sizes");
+// rl_moe_select_scored / rl_moe_route_scored: the routers above with the variants as arguments (softmax_all,
+// group_top 1 or 2, renorm; see moe_pick_sigmoid); the *_sigmoid entry points are (0, 2, 0).
+extern "C" int rl_moe_select_scored(const float* logits, int num_tokens, int num_experts, int top, const float* correction, int groups,
+                                    int keep, int softmax_all, int group_top, int renorm, int* ids, float* weights, cudaStream_t stream) {
+  RL_REQUIRE(num_tokens >= 0 && (group_top == 1 || group_top == 2), "rl_moe_select_scored: bad sizes or group_top %d", group_top);
   if (const int rc = moe_sigmoid_args("rl_moe_select_sigmoid", num_experts, top, groups, keep)) return rc;
   if (num_tokens == 0) return RL_OK;
   const size_t smem = (size_t)4 * ((num_experts + 3) & ~3) * sizeof(float);
-  rl_launch_pdl(moe_select_sigmoid_kernel, num_tokens, 32, smem, stream, logits, num_experts, top, correction, groups, keep, ids, weights);
+  rl_launch_pdl(moe_select_sigmoid_kernel, num_tokens, 32, smem, stream, logits, num_experts, top, correction, groups, keep, ids, weights,
+                softmax_all, group_top, renorm);
   RL_LAUNCH_CHECK("rl_moe_select_sigmoid");
   return RL_OK;
 }
 
-extern "C" int rl_moe_route_sigmoid(const void* x, int ldx, const void* router, const float* correction, int dtype, int num_tokens,
-                                    int hidden, int num_experts, int top, int groups, int keep, int* ids, float* weights,
-                                    cudaStream_t stream) {
-  RL_REQUIRE(num_tokens >= 0 && hidden > 0, "rl_moe_route_sigmoid: bad sizes M=%d d=%d", num_tokens, hidden);
+extern "C" int rl_moe_select_sigmoid(const float* logits, int num_tokens, int num_experts, int top, const float* correction, int groups,
+                                     int keep, int* ids, float* weights, cudaStream_t stream) {
+  return rl_moe_select_scored(logits, num_tokens, num_experts, top, correction, groups, keep, 0, 2, 0, ids, weights, stream);
+}
+
+extern "C" int rl_moe_route_scored(const void* x, int ldx, const void* router, const float* correction, int dtype, int num_tokens,
+                                   int hidden, int num_experts, int top, int groups, int keep, int softmax_all, int group_top, int renorm,
+                                   int* ids, float* weights, cudaStream_t stream) {
+  RL_REQUIRE(num_tokens >= 0 && hidden > 0 && (group_top == 1 || group_top == 2), "rl_moe_route_sigmoid: bad sizes M=%d d=%d", num_tokens, hidden);
   if (const int rc = moe_sigmoid_args("rl_moe_route_sigmoid", num_experts, top, groups, keep)) return rc;
   if (num_tokens == 0) return RL_OK;
   RL_REQUIRE(hidden + 4 * num_experts <= 11000, "rl_moe_route_sigmoid: hidden size plus four times the experts above 11,000");
   const size_t smem = (size_t)(4 * ((num_experts + 3) & ~3) + hidden) * sizeof(float);
   if (dtype == RL_F32)
     rl_launch_pdl(moe_route_sigmoid_kernel<float>, num_tokens, MOE_THREADS, smem, stream, (const float*)x, ldx, (const float*)router,
-                  correction, hidden, num_experts, top, groups, keep, ids, weights);
+                  correction, hidden, num_experts, top, groups, keep, ids, weights, softmax_all, group_top, renorm);
   else if (dtype == RL_BF16)
     rl_launch_pdl(moe_route_sigmoid_kernel<__nv_bfloat16>, num_tokens, MOE_THREADS, smem, stream, (const __nv_bfloat16*)x, ldx,
-                  (const __nv_bfloat16*)router, correction, hidden, num_experts, top, groups, keep, ids, weights);
+                  (const __nv_bfloat16*)router, correction, hidden, num_experts, top, groups, keep, ids, weights, softmax_all, group_top, renorm);
   else
     RL_REQUIRE(false, "rl_moe_route_sigmoid: unknown dtype %d", dtype);
   RL_LAUNCH_CHECK("rl_moe_route_sigmoid");
   return RL_OK;
+}
+
+extern "C" int rl_moe_route_sigmoid(const void* x, int ldx, const void* router, const float* correction, int dtype, int num_tokens,
+                                    int hidden, int num_experts, int top, int groups, int keep, int* ids, float* weights,
+                                    cudaStream_t stream) {
+  return rl_moe_route_scored(x, ldx, router, correction, dtype, num_tokens, hidden, num_experts, top, groups, keep, 0, 2, 0, ids, weights,
+                             stream);
 }
 
 // ------------------------------------------------------------------ gate and up of the chosen experts

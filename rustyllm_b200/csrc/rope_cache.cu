@@ -24,7 +24,8 @@ __global__ void __launch_bounds__(ROPE_THREADS)
 rope_kv_write_kernel(T* __restrict__ qkv, int ld, const int* __restrict__ positions,
                      const int* __restrict__ slot_of_token, const int* __restrict__ page_table, int max_pages,
                      const float* __restrict__ inv_freq, int H, int G, int hd, int vd, int rot, int interleaved,
-                     T* __restrict__ k_pool, T* __restrict__ v_pool, int write_cache) {
+                     T* __restrict__ k_pool, T* __restrict__ v_pool, int write_cache, const T* __restrict__ v_other, int ld_other,
+                     const float* __restrict__ v_mix) {
   rl_pdl_trigger();
   rl_pdl_wait();
   const int m = blockIdx.x;
@@ -58,6 +59,15 @@ rope_kv_write_kernel(T* __restrict__ qkv, int ld, const int* __restrict__ positi
       const float x0 = y0, x1 = y1;
       y0 = x0 * c - x1 * s;
       y1 = x0 * s + x1 * c;
+    }
+    const bool blend = is_v && v_other != nullptr;
+    if (blend) {
+      // values blended with another layer's values of the same token before they are cached (and left so in the row)
+      const float lam = *v_mix;
+      const T* o = v_other + (size_t)m * ld_other + (size_t)(hs - H - G) * vd;
+      y0 = (1.0f - lam) * y0 + lam * rl_ld(o + i0);
+      y1 = (1.0f - lam) * y1 + lam * rl_ld(o + i1);
+      rl_st(x + i0, y0); rl_st(x + i1, y1);
     }
     if (hs < H) {
       if (rotate) { rl_st(x + i0, y0); rl_st(x + i1, y1); }
@@ -153,11 +163,15 @@ kv_write_copy_kernel(const uint4* __restrict__ qkv, int ld16, const int* __restr
 // rotated keys go to k_pool [pages, G, RL_PAGE, head_dim] and the values to v_pool
 // [pages, G, RL_PAGE, value_dim] (same dtype as qkv).  With k_pool == nullptr nothing is
 // cached and the keys are rotated in place as well.
-extern "C" int rl_rope_kv_write(void* qkv, int dtype, int ld, const int* positions,
-                                const int* slot_of_token, const int* page_table, int max_pages,
-                                const float* inv_freq, int num_tokens, int num_heads, int num_kv_heads,
-                                int head_dim, int value_dim, int rotary_dim, int interleaved, void* k_pool,
-                                void* v_pool, cudaStream_t stream) {
+//
+// rl_rope_kv_write_mixed: the same, and where `v_other` is given ([M, ld_other] in the same dtype, G value heads a
+// row, e.g. the values an earlier layer made of the same tokens) the values become (1 - lam) v + lam v_other with
+// lam = *v_mix (a float on the device), computed in 32-bit, before they are cached.
+extern "C" int rl_rope_kv_write_mixed(void* qkv, int dtype, int ld, const int* positions,
+                                      const int* slot_of_token, const int* page_table, int max_pages,
+                                      const float* inv_freq, int num_tokens, int num_heads, int num_kv_heads,
+                                      int head_dim, int value_dim, int rotary_dim, int interleaved, void* k_pool,
+                                      void* v_pool, const void* v_other, int ld_other, const float* v_mix, cudaStream_t stream) {
   RL_REQUIRE(num_tokens >= 0 && num_heads > 0 && num_kv_heads > 0, "rl_rope_kv_write: bad sizes");
   RL_REQUIRE(head_dim > 0 && head_dim <= 256, "rl_rope_kv_write: head_dim %d outside (0, 256]", head_dim);
   RL_REQUIRE(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
@@ -165,19 +179,20 @@ extern "C" int rl_rope_kv_write(void* qkv, int dtype, int ld, const int* positio
   RL_REQUIRE(value_dim > 0 && value_dim <= 256 && value_dim % 2 == 0, "rl_rope_kv_write: value_dim %d must be even and in (0, 256]", value_dim);
   RL_REQUIRE(ld >= (num_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim, "rl_rope_kv_write: row stride %d too small", ld);
   RL_REQUIRE((k_pool == nullptr) == (v_pool == nullptr), "rl_rope_kv_write: give both cache pools or none");
+  RL_REQUIRE(v_other == nullptr || (v_mix != nullptr && ld_other >= num_kv_heads * value_dim), "rl_rope_kv_write: values to blend without a factor, or rows too short");
   if (num_tokens == 0) return RL_OK;
   const int write_cache = k_pool != nullptr;
   RL_REQUIRE(head_dim % 2 == 0, "rl_rope_kv_write: head_dim %d must be even", head_dim);
   const dim3 grid(num_tokens, (num_heads + 2 * num_kv_heads + ROPE_HEADS_PER_CTA - 1) / ROPE_HEADS_PER_CTA);
   const int threads = ROPE_THREADS;
   const int esz = dtype == RL_F32 ? 4 : 2;
-  if (rotary_dim == 0 && !write_cache) return RL_OK;          // nothing to rotate, nothing to store
-  if (rotary_dim == 0 && (dtype == RL_F32 || dtype == RL_BF16) && (head_dim * esz) % 16 == 0 && (value_dim * esz) % 16 == 0 &&
+  if (rotary_dim == 0 && !write_cache && v_other == nullptr) return RL_OK;          // nothing to rotate, nothing to store
+  if (v_other == nullptr && rotary_dim == 0 && (dtype == RL_F32 || dtype == RL_BF16) && (head_dim * esz) % 16 == 0 && (value_dim * esz) % 16 == 0 &&
       (ld * esz) % 16 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0)
     rl_launch_pdl(kv_write_copy_kernel, dim3(num_tokens), threads, 0, stream, (const uint4*)qkv, ld * esz / 16, positions,
                   slot_of_token, page_table, max_pages, num_heads * head_dim * esz / 16, num_kv_heads, head_dim * esz / 16,
                   value_dim * esz / 16, (uint4*)k_pool, (uint4*)v_pool);
-  else if (dtype == RL_BF16 && write_cache && !interleaved && rotary_dim == head_dim && value_dim == head_dim && head_dim % 16 == 0 && ld % 8 == 0 &&
+  else if (v_other == nullptr && dtype == RL_BF16 && write_cache && !interleaved && rotary_dim == head_dim && value_dim == head_dim && head_dim % 16 == 0 && ld % 8 == 0 &&
       ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0)
     rl_launch_pdl(rope_kv_write_bf16_half_kernel,
                   dim3(num_tokens, (num_heads + 2 * num_kv_heads + ROPE_FAST_HEADS_PER_CTA - 1) / ROPE_FAST_HEADS_PER_CTA),
@@ -187,13 +202,24 @@ extern "C" int rl_rope_kv_write(void* qkv, int dtype, int ld, const int* positio
   else if (dtype == RL_F32)
     rl_launch_pdl(rope_kv_write_kernel<float>, grid, threads, 0, stream,
         (float*)qkv, ld, positions, slot_of_token, page_table, max_pages, inv_freq, num_heads,
-        num_kv_heads, head_dim, value_dim, rotary_dim, interleaved, (float*)k_pool, (float*)v_pool, write_cache);
+        num_kv_heads, head_dim, value_dim, rotary_dim, interleaved, (float*)k_pool, (float*)v_pool, write_cache,
+        (const float*)v_other, ld_other, v_mix);
   else if (dtype == RL_BF16)
     rl_launch_pdl(rope_kv_write_kernel<__nv_bfloat16>, grid, threads, 0, stream,
         (__nv_bfloat16*)qkv, ld, positions, slot_of_token, page_table, max_pages, inv_freq, num_heads,
-        num_kv_heads, head_dim, value_dim, rotary_dim, interleaved, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, write_cache);
+        num_kv_heads, head_dim, value_dim, rotary_dim, interleaved, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, write_cache,
+        (const __nv_bfloat16*)v_other, ld_other, v_mix);
   else
     RL_REQUIRE(false, "rl_rope_kv_write: unknown dtype %d", dtype);
   RL_LAUNCH_CHECK("rl_rope_kv_write");
   return RL_OK;
+}
+
+extern "C" int rl_rope_kv_write(void* qkv, int dtype, int ld, const int* positions,
+                                const int* slot_of_token, const int* page_table, int max_pages,
+                                const float* inv_freq, int num_tokens, int num_heads, int num_kv_heads,
+                                int head_dim, int value_dim, int rotary_dim, int interleaved, void* k_pool,
+                                void* v_pool, cudaStream_t stream) {
+  return rl_rope_kv_write_mixed(qkv, dtype, ld, positions, slot_of_token, page_table, max_pages, inv_freq, num_tokens, num_heads,
+                                num_kv_heads, head_dim, value_dim, rotary_dim, interleaved, k_pool, v_pool, nullptr, 0, nullptr, stream);
 }

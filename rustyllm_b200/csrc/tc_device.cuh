@@ -8,7 +8,9 @@
 #include "common.cuh"
 
 // TC_OUT_GELU: as TC_OUT_BF16, the stored value being the tanh form of gelu of the product (plus bias)
-enum { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_ADD_F32 = 2, TC_OUT_SWIGLU = 3, TC_OUT_ROPE_KV = 4, TC_OUT_GELU = 5 };
+// TC_OUT_GEGLU: as TC_OUT_SWIGLU with the tanh form of gelu on the gate instead of silu
+enum { TC_OUT_BF16 = 0, TC_OUT_F32 = 1, TC_OUT_ADD_F32 = 2, TC_OUT_SWIGLU = 3, TC_OUT_ROPE_KV = 4, TC_OUT_GELU = 5, TC_OUT_GEGLU = 6 };
+__host__ __device__ __forceinline__ bool tc_out_gated(int out_mode) { return out_mode == TC_OUT_SWIGLU || out_mode == TC_OUT_GEGLU; }
 
 // silu(g) * u for a result that is stored in bf16: the fast exponential and division are
 // accurate to a few units in the last place of a float, far below bf16's rounding step
@@ -18,6 +20,7 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
   return z * __fdividef(1.0f, 1.0f + __expf(-2.0f * y));
 }
 __device__ __forceinline__ float silu_mul(float g, float u) { return g * __fdividef(1.0f, 1.0f + __expf(-g)) * u; }
+__device__ __forceinline__ float gated_mul(float g, float u, int out_mode) { return out_mode == TC_OUT_GEGLU ? gelu_tanh_f(g) * u : silu_mul(g, u); }
 
 // The optional norm work of an epilogue.
 struct TcFuse {
@@ -275,10 +278,10 @@ __device__ __forceinline__ void tc_finish_column(float4 v, int j, int r4, int la
           }
           break;
         }
-        if (out_mode == TC_OUT_SWIGLU) {      // v = (gate, up, gate, up) of output columns nn/2 and nn/2 + 1
+        if (tc_out_gated(out_mode)) {      // v = (gate, up, gate, up) of output columns nn/2 and nn/2 + 1
           __nv_bfloat16* ob = (__nv_bfloat16*)out + (size_t)(m0 + j) * ldo + (nn >> 1);
-          if (nn + 1 < N) ob[0] = __float2bfloat16_rn(silu_mul(v.x, v.y));
-          if (nn + 3 < N) ob[1] = __float2bfloat16_rn(silu_mul(v.z, v.w));
+          if (nn + 1 < N) ob[0] = __float2bfloat16_rn(gated_mul(v.x, v.y, out_mode));
+          if (nn + 3 < N) ob[1] = __float2bfloat16_rn(gated_mul(v.z, v.w, out_mode));
           break;
         }
         const size_t o = (size_t)(m0 + j) * ldo + nn;

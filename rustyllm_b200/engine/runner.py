@@ -104,9 +104,9 @@ class Runner:
         compute = parse_dtype(dtype)
         cfg_dict = read_config_json(path)
         arch = resolve_architecture(cfg_dict)
-        config = arch.parse_config(cfg_dict)
-        spec = arch.build_spec(config)
         ckpt = Checkpoint(path)
+        config = arch.parse_for(cfg_dict, {n: tuple(e.shape) for n, e in ckpt.entries.items()})
+        spec = arch.build_spec(config)
         t_parse = time.perf_counter()
         model = DecoderModel(spec, Runtime(dev, compute))
         from ..weights.loader import check_checkpoint

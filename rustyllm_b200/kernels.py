@@ -18,6 +18,7 @@ from .csrc import build as _build
 F32, BF16 = 0, 1
 OUT_SAME, OUT_F32, OUT_ADD_F32, OUT_SWIGLU = 0, 1, 2, 3
 OUT_GELU = 5        # the tensor-core product alone: bf16 out = gelu_tanh(product)
+OUT_GEGLU = 6       # the tensor-core product alone: as OUT_SWIGLU with gelu_tanh on the gate
 
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
@@ -40,6 +41,23 @@ _SIGNATURES = {
     "rl_random_fill": [_c_void_p, _c_int, _c_ll, ctypes.c_ulonglong, _c_float, _c_float, _c_void_p],
     "rl_gemm_simt": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                      _c_int, _c_int, _c_void_p],
+    "rl_layer_norm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
+    "rl_token_shift_mix": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll,
+                           _c_void_p, _c_int, _c_int, _c_void_p],
+    "rl_tanh_cast": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
+    "rl_scaled_add": [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_float, _c_ll, _c_void_p],
+    "rl_row_gate_add": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "rl_scale": [_c_void_p, _c_ll, _c_float, _c_void_p],
+    "rl_geglu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "rl_channel_decay_scan": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                              _c_void_p, _c_int, _c_void_p, _c_ll, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "rl_moe_route_scored": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                            _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    "rl_moe_select_scored": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
+                             _c_void_p],
+    "rl_rope_kv_write_mixed": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
+                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                               _c_void_p, _c_void_p],
     "rl_rope_kv_write": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
     "rl_attention_simt": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
@@ -487,10 +505,12 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_of_token: torch.Tensor,
                   page_table: torch.Tensor, inv_freq: torch.Tensor, num_heads: int, num_kv_heads: int,
                   head_dim: int, rotary_dim: int, interleaved: bool,
-                  k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], value_dim: Optional[int] = None) -> None:
+                  k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], value_dim: Optional[int] = None,
+                  v_other: Optional[torch.Tensor] = None, v_mix: Optional[torch.Tensor] = None) -> None:
     """Rotates the query and key heads of qkv ([M, H*hd + G*hd + G*vd]) in place and writes keys
     and values at their tokens' places of the paged pools.  ``value_dim`` (default: head_dim)
-    is the width of a value head."""
+    is the width of a value head.  ``v_other`` [M, G*vd] (a view is fine) with ``v_mix`` (a float32 scalar on the
+    device): the values become (1 - v_mix) v + v_mix v_other, in 32-bit, before they are cached."""
     vd = head_dim if value_dim is None else value_dim
     _need(qkv, "qkv"); _need(positions, "positions", torch.int32)
     _need(inv_freq, "inv_freq", torch.float32)
@@ -504,10 +524,15 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_of_token: tor
     else:
         max_pages = 0
     assert inv_freq.numel() >= rotary_dim // 2
-    _check(library().rl_rope_kv_write(
+    ld_other = 0
+    if v_other is not None:
+        _need(v_other, "v_other", qkv.dtype, contiguous=False); _need(v_mix, "v_mix", torch.float32)
+        assert v_other.shape == (M, num_kv_heads * vd) and v_other.stride(1) == 1 and v_mix.numel() == 1
+        ld_other = v_other.stride(0) if M > 1 else num_kv_heads * vd
+    _check(library().rl_rope_kv_write_mixed(
         qkv.data_ptr(), _dt(qkv), qkv.stride(0), positions.data_ptr(), _ptr(slot_of_token), _ptr(page_table),
         max_pages, inv_freq.data_ptr(), M, num_heads, num_kv_heads, head_dim, vd, rotary_dim, int(interleaved),
-        _ptr(k_pool), _ptr(v_pool), _stream()), "rl_rope_kv_write")
+        _ptr(k_pool), _ptr(v_pool), _ptr(v_other), ld_other, _ptr(v_mix) if v_other is not None else None, _stream()), "rl_rope_kv_write")
     _count()
 
 
@@ -547,6 +572,92 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
         float(softcap or 0.0), int(keep_first or 0), int(chunk or 0), head_dim if values_in_keys else 0,
         int(bool(gate_per_head)), _stream()),
         "rl_attention_simt")
+    _count()
+
+
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None,
+               weight2: Optional[torch.Tensor] = None, out2: Optional[torch.Tensor] = None) -> None:
+    """out[r] = (x[r] - mean) / sqrt(mean of squared deviations + eps) * weight (x[rows[r]] if rows is given); with
+    ``weight2`` and ``out2``: also the same row's norm times the second weight, from one read of x."""
+    _need(x, "x", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out")
+    d = x.shape[-1]
+    n = out.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        assert rows.numel() == n
+    else:
+        assert x.shape[0] == n
+    assert weight.numel() == d and out.shape[-1] == d
+    if (weight2 is None) != (out2 is None):
+        raise KernelError("layer_norm: a second weight and a second output come together")
+    if out2 is not None:
+        _need(weight2, "weight2", torch.float32); _need(out2, "out2", out.dtype)
+        assert weight2.numel() == d and out2.shape == out.shape
+    _check(library().rl_layer_norm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), _ptr(weight2), _ptr(out2), _dt(out), _ptr(rows), n, d,
+                                   float(eps), _stream()), "rl_layer_norm")
+    _count()
+
+
+def geglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
+    """out = gelu_tanh(gate) * up; layouts as for ``swiglu``."""
+    _need(gate_up, "gate_up"); _need(out, "out", gate_up.dtype)
+    M, two_i = gate_up.shape
+    assert two_i % 2 == 0 and out.shape == (M, two_i // 2)
+    _check(library().rl_geglu(gate_up.data_ptr(), out.data_ptr(), _dt(out), M, two_i // 2, int(interleaved), _stream()), "rl_geglu")
+    _count()
+
+
+def token_shift_mix(h: torch.Tensor, mu: torch.Tensor, positions: torch.Tensor, slot_of_token: torch.Tensor, cu_seqlens: torch.Tensor,
+                    state: torch.Tensor, out: torch.Tensor) -> None:
+    """out[s, m] = h[m] + (previous(m) - h[m]) * mu[s] for the n rows of ``mu`` (float32 [n, d]); previous(m) is the
+    row in front where it belongs to the same sequence, else the sequence's state (float [d] a slot; zero at position
+    0).  Leaves every sequence's last row of the step in its state.  h [M, d] (a view is fine), out [n, M, d]."""
+    _need(h, "h", contiguous=False); _need(mu, "mu", torch.float32); _need(out, "out", h.dtype)
+    _need(positions, "positions", torch.int32); _need(slot_of_token, "slot_of_token", torch.int32); _need(cu_seqlens, "cu_seqlens", torch.int32)
+    M, d = h.shape
+    n = mu.shape[0]
+    assert mu.shape == (n, d) and out.shape == (n, M, d) and h.stride(1) == 1
+    sp, ss = _state_args(state)
+    assert state.shape[1] >= 4 * d
+    _check(library().rl_token_shift_mix(h.data_ptr(), h.stride(0) if M > 1 else d, _dt(h), mu.data_ptr(), n, positions.data_ptr(),
+                                        slot_of_token.data_ptr(), cu_seqlens.data_ptr(), cu_seqlens.numel() - 1, sp, ss, out.data_ptr(),
+                                        M, d, _stream()), "rl_token_shift_mix")
+    _count()
+
+
+def tanh_cast(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = tanh(x); x float32, out in its own dtype."""
+    _need(x, "x", torch.float32); _need(out, "out")
+    assert out.numel() == x.numel()
+    _check(library().rl_tanh_cast(x.data_ptr(), out.data_ptr(), _dt(out), x.numel(), _stream()), "rl_tanh_cast")
+    _count()
+
+
+def scaled_add(x: torch.Tensor, y0: torch.Tensor, s0: float, y1: Optional[torch.Tensor] = None, s1: float = 0.0) -> None:
+    """x += s0 * y0 + s1 * y1, all float32 of one shape (``y1`` may be ``None``)."""
+    _need(x, "x", torch.float32); _need(y0, "y0", torch.float32)
+    assert y0.shape == x.shape
+    if y1 is not None:
+        _need(y1, "y1", torch.float32)
+        assert y1.shape == x.shape
+    _check(library().rl_scaled_add(x.data_ptr(), y0.data_ptr(), float(s0), _ptr(y1), float(s1), x.numel(), _stream()), "rl_scaled_add")
+    _count()
+
+
+def row_gate_add(x: torch.Tensor, y: torch.Tensor, h: torch.Tensor, gate: torch.Tensor) -> None:
+    """x[m] += sigmoid(h[m] . gate) * y[m]; x, y float32 [M, d]; h [M, d] and gate [d] in the compute dtype."""
+    _need(x, "x", torch.float32); _need(y, "y", torch.float32); _need(h, "h", contiguous=False); _need(gate, "gate", h.dtype)
+    M, d = x.shape
+    assert y.shape == (M, d) and h.shape == (M, d) and gate.numel() == d and h.stride(1) == 1
+    _check(library().rl_row_gate_add(x.data_ptr(), y.data_ptr(), h.data_ptr(), h.stride(0) if M > 1 else d, gate.data_ptr(), _dt(h), M, d,
+                                     _stream()), "rl_row_gate_add")
+    _count()
+
+
+def scale(y: torch.Tensor, s: float) -> None:
+    """y *= s in place (float32)."""
+    _need(y, "y", torch.float32)
+    _check(library().rl_scale(y.data_ptr(), y.numel(), float(s), _stream()), "rl_scale")
     _count()
 
 
@@ -756,6 +867,29 @@ def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Te
     _count()
 
 
+def channel_decay_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, wlog: torch.Tensor, bonus: torch.Tensor, out: torch.Tensor,
+                       state: torch.Tensor, cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, num_heads: int, dk: int, dv: int) -> None:
+    """out_t = (S_{t-1} + diag(bonus[h]) k_t v_t^T)^T q_t, then S_t = diag(w_t) S_{t-1} + k_t v_t^T with
+    w_t = exp(-exp(wlog_t)), for every head of every sequence of the step; the state (float [H, dv, dk] a slot) is read
+    from and left in ``state``.  q, k [M, H * dk], v [M, H * dv] (views are fine), wlog float32 [M, H * dk], bonus
+    float32 [H, dk], out float32 [M, H * dv]."""
+    for t, name in ((q, "q"), (k, "k"), (v, "v")):
+        _need(t, name, q.dtype, contiguous=False)
+        assert t.stride(1) == 1
+    _need(out, "out", torch.float32); _need(wlog, "wlog", torch.float32, contiguous=False); _need(bonus, "bonus", torch.float32)
+    _need(cu_seqlens, "cu_seqlens", torch.int32); _need(seq_slots, "seq_slots", torch.int32)
+    M = out.shape[0]
+    assert out.shape == (M, num_heads * dv) and q.shape == (M, num_heads * dk) and k.shape == q.shape and v.shape == (M, num_heads * dv)
+    assert wlog.shape == (M, num_heads * dk) and wlog.stride(1) == 1 and bonus.numel() == num_heads * dk
+    sp, ss = _state_args(state)
+    assert state.shape[1] >= 4 * num_heads * dk * dv
+    _check(library().rl_channel_decay_scan(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), _dt(q),
+                                           wlog.data_ptr(), wlog.stride(0), bonus.data_ptr(), cu_seqlens.data_ptr(), seq_slots.data_ptr(),
+                                           seq_slots.numel(), sp, ss, out.data_ptr(), out.stride(0), num_heads, dk, dv,
+                                           int(M >= 4 * seq_slots.numel()), _stream()), "rl_channel_decay_scan")
+    _count()
+
+
 def norm_add(x: torch.Tensor, y0: torch.Tensor, s0: float, y1: Optional[torch.Tensor], s1: float, weight: torch.Tensor, eps: float,
              x_bf16: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> None:
     """x += out_scale * rms_norm(s0 * y0 + s1 * y1) * weight, all float32 [M, d] (``y1`` may be ``None``); ``x_bf16``:
@@ -830,6 +964,37 @@ def moe_select_sigmoid(logits: torch.Tensor, correction: Optional[torch.Tensor],
                                            weights.data_ptr(), _stream()), "rl_moe_select_sigmoid")
     _count()
 
+
+
+def moe_route_scored(x: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int,
+                     ids: torch.Tensor, weights: torch.Tensor, softmax_all: bool, group_top: int, renorm: bool) -> None:
+    """``moe_route_sigmoid`` with its variants as arguments: ``softmax_all`` - scores are the softmax of the logits over
+    all experts; ``group_top`` - a group's score is the sum of its 1 or 2 largest choice scores; ``renorm`` - the
+    weights are the chosen scores over their sum (+ 1e-20)."""
+    _need(x, "x", contiguous=False); _need(router, "router", x.dtype); _need(ids, "ids", torch.int32)
+    _need(weights, "weights", torch.float32)
+    M, d = x.shape
+    E = router.shape[0]
+    assert router.shape == (E, d) and ids.shape == (M, top) and weights.shape == (M, top) and x.stride(1) == 1
+    if correction is not None:
+        _need(correction, "correction", torch.float32)
+        assert correction.numel() == E
+    _check(library().rl_moe_route_scored(x.data_ptr(), x.stride(0) if M > 1 else d, router.data_ptr(), _ptr(correction), _dt(x), M, d,
+                                         E, int(top), int(groups), int(keep), int(bool(softmax_all)), int(group_top), int(bool(renorm)),
+                                         ids.data_ptr(), weights.data_ptr(), _stream()), "rl_moe_route_scored")
+    _count()
+
+
+def moe_select_scored(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int,
+                      ids: torch.Tensor, weights: torch.Tensor, softmax_all: bool, group_top: int, renorm: bool) -> None:
+    """``moe_route_scored``'s second half alone, from float32 logits [M, E]."""
+    _need(logits, "logits", torch.float32); _need(ids, "ids", torch.int32); _need(weights, "weights", torch.float32)
+    M, E = logits.shape
+    assert ids.shape == (M, top) and weights.shape == (M, top)
+    _check(library().rl_moe_select_scored(logits.data_ptr(), M, E, int(top), _ptr(correction), int(groups), int(keep),
+                                          int(bool(softmax_all)), int(group_top), int(bool(renorm)), ids.data_ptr(), weights.data_ptr(),
+                                          _stream()), "rl_moe_select_scored")
+    _count()
 
 
 def repeat_penalty(logits: torch.Tensor, recent: torch.Tensor, recent_len: torch.Tensor, penalty: float) -> None:
@@ -939,7 +1104,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_mode: int,
     M, K = a.shape
     N = w.shape[0]
     assert w.shape[1] == K and out.stride(1) == 1
-    if out_mode == OUT_SWIGLU:      # rows of w are (gate_0, up_0, gate_1, ...): out = silu(gate) * up, [M, N/2]
+    if out_mode in (OUT_SWIGLU, OUT_GEGLU):      # rows of w are (gate_0, up_0, gate_1, ...): out = act(gate) * up, [M, N/2]
         assert N % 2 == 0 and out.shape == (M, N // 2) and out.dtype == torch.bfloat16
     else:
         assert out.shape == (M, N)

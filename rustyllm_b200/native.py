@@ -70,7 +70,7 @@ def eligible(model, cache) -> bool:
     from .parts.rope import RotaryEmbedding
     if model.runtime.compute_dtype != torch.bfloat16 or model.runtime.device.type != "cuda" or cache.dtype != torch.bfloat16:
         return False
-    if model.injections or model.head.softcap is not None:
+    if model.injections or model.head.softcap is not None or getattr(model.head, "scale", 1.0) != 1.0:
         return False
     if type(model.embedding) is not TokenEmbedding or type(model.head) is not LMHead or type(model.final_norm) is not RMSNorm:
         return False
@@ -82,7 +82,7 @@ def eligible(model, cache) -> bool:
         if type(b.mixer_norm) is not RMSNorm or type(b.feed_forward_norm) is not RMSNorm or not isinstance(b.mixer.position, RotaryEmbedding):
             return False
         a, f = b.mixer, b.feed_forward
-        if a.sink or a.gated:
+        if a.sink or a.gated or getattr(a, "value_mix", None) or f.activation != "silu":
             return False
         if not (f.interleaved and _matrix_ok(a.wqkv) and _matrix_ok(a.wo) and _matrix_ok(f.wgu) and _matrix_ok(f.wdown)):
             return False

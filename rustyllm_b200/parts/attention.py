@@ -16,7 +16,11 @@ with one weight vector for all heads, before the rotation (``names["q_norm"]``, 
 visible behind a window (``keep_first``); a chunked mask instead of a window (``chunk`` = C: a query at position i
 sees j <= i with i // C == j // C, blocks counted from the sequence's start); query and key heads divided by their
 root mean square after the rotation, without a weight (``unit_qk_eps``); values that are the keys as projected,
-before rotation and norm, with no value projection (``value_from_key``).  Here Wq, Wk, Wv are one matrix [(H + 2G) hd x d] so that one product
+before rotation and norm, with no value projection (``value_from_key``); an output gate of one number a head
+instead of one an element (``gate_per_head``: Wg has H rows); values blended with another layer's values of the same
+token before they are cached, v <- (1 - lam) v + lam v_other (``value_mix`` = {"key": k, "role": "source" or "blend"}:
+the "source" layer of a key leaves its values of the step's tokens for the "blend" layers that run after it; lam is
+the learned scalar ``names["vmix"]``).  Here Wq, Wk, Wv are one matrix [(H + 2G) hd x d] so that one product
 serves all three, rotation and cache write are one kernel, and all tokens of the
 step (several sequences, prompt or single tokens) run together.
 """
@@ -43,7 +47,7 @@ class GQAttention(Mixer):
                  scale: Optional[float] = None, sink: bool = False, conv_taps: int = 0,
                  qk_norm_eps: Optional[float] = None, softcap: Optional[float] = None, keep_first: int = 0,
                  bias_o: Optional[bool] = None, chunk: Optional[int] = None, unit_qk_eps: Optional[float] = None,
-                 value_from_key: bool = False):
+                 value_from_key: bool = False, gate_per_head: bool = False, value_mix: Optional[Dict[str, str]] = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are no multiple of {num_kv_heads} KV heads")
         if head_dim % 2 or not (0 < head_dim <= 256):
@@ -57,8 +61,6 @@ class GQAttention(Mixer):
         self.runtime = runtime
         self.d, self.H, self.G, self.hd = hidden_size, num_heads, num_kv_heads, head_dim
         self.bias = bias
-        if bias and "g" in names:
-            raise ValueError("an output gate with biases is not built")
         self.window = window
         self.names = names
         self.scale = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)     # src/model.rs:7239
@@ -93,6 +95,19 @@ class GQAttention(Mixer):
             raise ValueError(f"values that are the keys need value_dim = head_dim, got {vd} and {head_dim}")
         if (self.value_from_key or self.unit_qk_eps is not None) and (bias or self.conv_taps or self.qk_norm):
             raise ValueError("unit-size heads or values from keys together with biases, a convolution or weighted head norms are not built")
+        self.gate_per_head = bool(gate_per_head)
+        if self.gate_per_head and not self.gated:
+            raise ValueError("gate_per_head needs an output gate (names['g'])")
+        self.gate_rows = 0 if not self.gated else (num_heads if self.gate_per_head else num_heads * vd)
+        if value_mix is not None:
+            if value_mix.get("role") not in ("source", "blend") or not value_mix.get("key"):
+                raise ValueError("value_mix needs a key and the role 'source' or 'blend'")
+            if value_mix["role"] == "blend" and "vmix" not in names:
+                raise ValueError("a layer that blends its values needs names['vmix']")
+            if self.value_from_key or self.conv_taps or self.qk_norm:
+                raise ValueError("blended values together with values from keys, a convolution or head norms are not built")
+        self.value_mix = dict(value_mix) if value_mix is not None else None
+        self.vmix = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         d, H, G, hd, vd, n = self.d, self.H, self.G, self.hd, self.vd, self.names
@@ -101,7 +116,7 @@ class GQAttention(Mixer):
         if not self.value_from_key:
             qkv += (ParamSource(n["v"] + sfx, (G * vd, d)),)
         if self.gated:
-            qkv += (ParamSource(n["g"] + sfx, (H * vd, d)),)
+            qkv += (ParamSource(n["g"] + sfx, (self.gate_rows, d)),)
         specs = {"wqkv": ParamSpec(qkv), "wo": ParamSpec((ParamSource(n["o"] + sfx, (d, H * vd)),))}
         bsfx = n.get("bias_suffix", ".bias")
         if self.bias:
@@ -114,11 +129,20 @@ class GQAttention(Mixer):
             csfx, t = n.get("conv_suffix", ".conv"), self.conv_taps
             specs["conv_w"] = ParamSpec((ParamSource(n["q"] + csfx, (H * hd, t)), ParamSource(n["k"] + csfx, (G * hd, t)),
                                          ParamSource(n["v"] + csfx, (G * vd, t))), role="vector")
+        if self.value_mix is not None and self.value_mix["role"] == "blend":
+            specs["vmix"] = ParamSpec((ParamSource(n["vmix"], ()),), role="vector", init="zeros")
         if "q_norm" in n:
             specs["q_norm_w"] = ParamSpec((ParamSource(n["q_norm"], (hd,)),), role="vector", init="ones")
         if "k_norm" in n:
             specs["k_norm_w"] = ParamSpec((ParamSource(n["k_norm"], (hd,)),), role="vector", init="ones")
         return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        b = tensors.get("bqkv")
+        if b is not None and self.gated:
+            # the gate's rows ride behind q, k, v in the one product and have no bias
+            tensors = dict(tensors, bqkv=torch.cat([b, torch.zeros(self.gate_rows, dtype=b.dtype, device=b.device)]))
+        super().bind(tensors)
 
     def kv_need(self) -> KVNeed:
         return KVNeed(self.G, self.hd, self.window, None if self.vd == self.hd else self.vd, self.keep_first, self.chunk)
@@ -144,7 +168,15 @@ class GQAttention(Mixer):
         M = xn.shape[0]
         dt = xn.dtype
         n_qkv = (H + G) * hd + (0 if self.value_from_key else G * vd)
-        qkv = torch.empty((M, n_qkv + (H * vd if self.gated else 0)), dtype=dt, device=xn.device)
+        qkv = torch.empty((M, n_qkv + self.gate_rows), dtype=dt, device=xn.device)
+        v_other = v_mix = None
+        if self.value_mix is not None and self.value_mix["role"] == "blend":
+            v_other = getattr(step, "derived", {}).get(("values", self.value_mix["key"]))
+            if v_other is None:
+                raise K.KernelError(f"no layer has left values under {self.value_mix['key']!r} in this step for this one to blend with")
+            if v_other.shape != (M, G * vd):
+                raise K.KernelError(f"values to blend with are {tuple(v_other.shape)}, this layer's {(M, G * vd)}")
+            v_mix = self.vmix
         group, layer = cache.kv_group, cache.kv_layer
         k_pool, v_pool = group.k_pool(layer), group.v_pool(layer)
         pos = self.position
@@ -172,7 +204,7 @@ class GQAttention(Mixer):
                           k_pool if cache.writes else None, v_pool if cache.writes else None)
             if self.conv_taps > 1 and cache.writes:
                 K.short_conv_state(qkv, self.conv_taps, step.cu_seqlens, step.seq_slots, cache.state)
-        elif (dt == torch.bfloat16 and vd == hd and not self.gated and self.wqkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
+        elif (v_other is None and dt == torch.bfloat16 and vd == hd and not self.gated and self.wqkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
                 and K.gemm_tc_qkv_rope_supported(x, self.wqkv, H, G, hd, pos.rotary_dim)):
             # few tokens: rotation and cache write ride in the product's epilogue
             kw = dict(row_sumsq=xn.sumsq, row_eps=xn.eps) if isinstance(xn, NormedInput) else {}
@@ -183,9 +215,13 @@ class GQAttention(Mixer):
             linear(xn, self.wqkv, qkv, OUT_SAME, self.bqkv)
             K.rope_kv_write(qkv, step.positions, step.slot_of_token, group.page_table, pos.inv_freq, H, G, hd,
                             pos.rotary_dim, pos.interleaved,
-                            k_pool if cache.writes else None, v_pool if cache.writes else None, value_dim=vd)
+                            k_pool if cache.writes else None, v_pool if cache.writes else None, value_dim=vd,
+                            v_other=v_other, v_mix=v_mix)
+        if self.value_mix is not None and self.value_mix["role"] == "source" and hasattr(step, "derived"):
+            # this layer's values of the step's tokens, as cached, for the layers that blend theirs with them
+            step.derived[("values", self.value_mix["key"])] = qkv[:, (H + G) * hd:(H + G) * hd + G * vd]
         attn = torch.empty((M, H * vd), dtype=dt, device=xn.device)
         K.attention(q, k_pool, v_pool, group.page_table, step, attn, H, G, hd, self.scale,
                     self.window or 0, value_dim=vd, sink=self.sink, gate=qkv[:, n_qkv:] if self.gated else None,
-                    softcap=self.softcap, keep_first=self.keep_first, chunk=self.chunk or 0)
+                    softcap=self.softcap, keep_first=self.keep_first, chunk=self.chunk or 0, gate_per_head=self.gate_per_head)
         return linear(attn, self.wo, residual, _out_mode, self.bo, then_norm=then_norm)

@@ -55,6 +55,41 @@ class PreNormBlock(Block):
         return None
 
 
+@register_block("parallel_pre_norm")
+class ParallelPreNormBlock(Block):
+    """A layer whose two sublayers both read norms of the same stream and join it together:
+
+        x += mixer(norm1(x)) + feed_forward(norm2(x))
+
+    Both norms are taken before either sublayer adds anything; two norms that can share a kernel
+    (``pairs_with`` / ``forward_with``: the row's statistics once, two weights) do.  A layer without a
+    feed-forward is x += mixer(norm1(x))."""
+
+    def __init__(self, runtime: Runtime, mixer: Mixer, mixer_norm: Norm, feed_forward: FeedForward,
+                 feed_forward_norm: Norm):
+        self.runtime = runtime
+        self.mixer, self.mixer_norm = mixer, mixer_norm
+        self.feed_forward, self.feed_forward_norm = feed_forward, feed_forward_norm
+
+    def sub_parts(self):
+        return {"mixer": self.mixer, "mixer_norm": self.mixer_norm,
+                "feed_forward": self.feed_forward, "feed_forward_norm": self.feed_forward_norm}
+
+    def forward(self, x: torch.Tensor, step, cache, pending=None, next_norm=None):
+        dt = self.runtime.compute_dtype
+        if getattr(self.feed_forward, "absent", False):
+            self.mixer.forward(self.mixer_norm.forward(x, dt), x, step, cache)
+            return None
+        pairs = getattr(self.mixer_norm, "pairs_with", None)
+        if pairs is not None and pairs(self.feed_forward_norm):
+            h1, h2 = self.mixer_norm.forward_with(self.feed_forward_norm, x, dt)
+        else:
+            h1, h2 = self.mixer_norm.forward(x, dt), self.feed_forward_norm.forward(x, dt)
+        self.mixer.forward(h1, x, step, cache)
+        self.feed_forward.forward(h2, x, step)
+        return None
+
+
 @register_block("post_norm")
 class PostNormBlock(Block):
     """A layer whose sublayers read the stream itself and whose norms sit on what they return:

@@ -101,9 +101,10 @@ class ScaledPairEmbedding(TokenEmbedding):
 @register("head", "lm_head")
 class LMHead(Part):
     def __init__(self, runtime: Runtime, vocab_size: int, hidden_size: int, name: str,
-                 tied_to: Optional[str] = None, softcap: Optional[float] = None):
+                 tied_to: Optional[str] = None, softcap: Optional[float] = None, scale: float = 1.0):
         if softcap is not None and not softcap > 0:
             raise ValueError(f"softcap {softcap} must be > 0 or None")
+        self.scale = float(scale)        # logits <- logits * scale (a constant of the model), before any soft cap
         self.softcap = None if softcap is None else float(softcap)    # logits <- cap * tanh(logits / cap)
         self.runtime = runtime
         self.V, self.d, self.name, self.tied_to = vocab_size, hidden_size, name, tied_to
@@ -117,6 +118,8 @@ class LMHead(Part):
         """xn: [W, d] compute dtype -> float32 logits [W, V]."""
         logits = torch.empty((xn.shape[0], self.V), dtype=torch.float32, device=xn.device)
         linear(xn, self.weight, logits, OUT_F32)
+        if self.scale != 1.0:
+            K.scale(logits, self.scale)
         if self.softcap is not None:
             K.softcap(logits, self.softcap)
         return logits

@@ -25,8 +25,9 @@ from .registry import register_feed_forward
 class GatedMLP(FeedForward):
     def __init__(self, runtime: Runtime, hidden_size: int, intermediate_size: int, names: Dict[str, str],
                  activation: str = "silu", bias: bool = False):
-        if activation != "silu":
-            raise ValueError(f"activation {activation!r} is not supported; known: 'silu'")
+        if activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"activation {activation!r} is not supported; known: 'silu', 'gelu_tanh'")
+        self.activation = activation       # on the gate: silu(g) * u, or the tanh form of gelu, gelu_tanh(g) * u
         self.runtime = runtime
         self.d, self.I = hidden_size, intermediate_size
         self.names = names
@@ -54,21 +55,28 @@ class GatedMLP(FeedForward):
     def takes_normed_input(self, num_tokens: int) -> bool:
         return self.interleaved and can_fold_norms(self.wgu, self.runtime.compute_dtype, num_tokens)
 
-    def forward(self, xn, residual: torch.Tensor, step, then_norm=None):
+    def forward_out(self, xn, step):
+        """The output as float32 [M, d] of its own (for whoever scales it before it joins the stream)."""
+        y = torch.empty((xn.shape[0], self.d), dtype=torch.float32, device=xn.device)
+        self.forward(xn, y, step, _out_mode=K.OUT_F32)
+        return [(y, 1.0)]
+
+    def forward(self, xn, residual: torch.Tensor, step, then_norm=None, _out_mode=OUT_ADD_F32):
         M = xn.shape[0]
         h = torch.empty((M, self.I), dtype=xn.dtype, device=xn.device)
+        gelu = self.activation == "gelu_tanh"
         # The activation runs in the product's epilogue: with few tokens the kernel streams
         # weights and the epilogue is idle time anyway; with many, the persistent kernel drains
         # one accumulator while the tensor cores fill the other.
         x = xn.weighted if isinstance(xn, NormedInput) else xn
         if self.interleaved and self.wgu.dtype == torch.bfloat16 and K.gemm_tc_supported(x, self.wgu, None):
             kw = dict(row_sumsq=xn.sumsq, row_eps=xn.eps) if isinstance(xn, NormedInput) else {}
-            K.gemm_tc(x, self.wgu, h, K.OUT_SWIGLU, self.bgu, **kw)
+            K.gemm_tc(x, self.wgu, h, K.OUT_GEGLU if gelu else K.OUT_SWIGLU, self.bgu, **kw)
         else:
             gu = torch.empty((M, 2 * self.I), dtype=xn.dtype, device=xn.device)
             linear(xn, self.wgu, gu, OUT_SAME, self.bgu)
-            K.swiglu(gu, h, interleaved=self.interleaved)
-        return linear(h, self.wdown, residual, OUT_ADD_F32, self.bdown, then_norm=then_norm)
+            (K.geglu if gelu else K.swiglu)(gu, h, interleaved=self.interleaved)
+        return linear(h, self.wdown, residual, _out_mode, self.bdown, then_norm=then_norm)
 
 
 @register_feed_forward("dense_mlp")

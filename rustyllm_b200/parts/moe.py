@@ -38,15 +38,18 @@ class MoEMLP(FeedForward):
             raise ValueError(f"top {top} must lie in [1, {num_experts}]")
         if top > 32:
             raise ValueError("at most 32 experts a token")
-        if scoring not in ("softmax", "sigmoid"):
-            raise ValueError(f"scoring {scoring!r} is not known; known: 'softmax', 'sigmoid'")
+        if scoring not in ("softmax", "sigmoid", "softmax_all"):
+            raise ValueError(f"scoring {scoring!r} is not known; known: 'softmax', 'sigmoid', 'softmax_all'")
+        # "softmax_all": scores s = softmax(z) over all experts; the ``top`` largest are chosen among the ``keep_groups``
+        # best of ``groups`` equal groups of neighbours (a group's score: its largest score); the weights are the chosen
+        # scores divided by their sum (+ 1e-20)
         # "sigmoid": scores s = sigmoid(z); experts are chosen by s + correction (``names["correction"]``, a value an
         # expert) among the ``keep_groups`` best of ``groups`` equal groups of neighbours (a group's score: its two
         # largest choice scores); the weights are the chosen experts' s, not renormalised
         self.scoring, self.groups, self.keep_groups = scoring, int(groups), int(keep_groups)
-        if scoring == "sigmoid":
+        if scoring in ("sigmoid", "softmax_all"):
             if router_bias:
-                raise ValueError("a router with sigmoid scores has a correction of the choice, not a bias")
+                raise ValueError(f"a router with {scoring} scores has no bias (sigmoid scores may have a correction of the choice)")
             if groups < 1 or num_experts % groups or not (1 <= keep_groups <= groups):
                 raise ValueError(f"{groups} groups (keep {keep_groups}) do not fit {num_experts} experts")
             if keep_groups * (num_experts // groups) < top:
@@ -59,6 +62,13 @@ class MoEMLP(FeedForward):
         self.names = names
         self.router_bias = router_bias
         self.shared = build_part("feed_forward", shared, runtime) if shared is not None else None
+        # names["shared_gate"] (a [1, d] matrix): the shared expert's output times sigmoid(gate . xn), one number a token
+        self.shared_gated = "shared_gate" in names
+        if self.shared_gated and self.shared is None:
+            raise ValueError("a gate of the shared expert without a shared expert")
+        if self.shared_gated and not hasattr(self.shared, "forward_out"):
+            raise ValueError("a gated shared expert must return its output (forward_out)")
+        self.shared_gate = None
         self.interleaved = runtime.compute_dtype == torch.bfloat16
         self.router = self.router_b = self.wgu = self.wdown = None
 
@@ -77,6 +87,8 @@ class MoEMLP(FeedForward):
         }
         if self.scoring == "sigmoid" and "correction" in n:
             specs["correction"] = ParamSpec((ParamSource(n["correction"], (E,)),), role="vector", init="zeros")
+        if self.shared_gated:
+            specs["shared_gate"] = ParamSpec((ParamSource(n["shared_gate"] + sfx, (1, d)),))
         if self.router_bias:
             specs["router_b"] = ParamSpec((ParamSource(n["router"] + n.get("bias_suffix", ".bias"), (E,)),),
                                           role="vector", init="zeros")
@@ -103,13 +115,15 @@ class MoEMLP(FeedForward):
         router = self.router
         if router.dtype != xn.dtype:
             raise K.KernelError(f"the router's matrix is {router.dtype} in a {xn.dtype} run")
-        if self.scoring == "sigmoid":
+        if self.scoring in ("sigmoid", "softmax_all"):
+            variant = dict(softmax_all=self.scoring == "softmax_all", group_top=1 if self.scoring == "softmax_all" else 2,
+                           renorm=self.scoring == "softmax_all")
             if M >= self.ROUTER_PRODUCT_FROM:
                 logits = torch.empty((M, self.E), dtype=torch.float32, device=xn.device)
                 linear(xn, router, logits, OUT_F32)
-                K.moe_select_sigmoid(logits, self.correction, self.top, self.groups, self.keep_groups, ids, weights)
+                K.moe_select_scored(logits, self.correction, self.top, self.groups, self.keep_groups, ids, weights, **variant)
             else:
-                K.moe_route_sigmoid(xn, router, self.correction, self.top, self.groups, self.keep_groups, ids, weights)
+                K.moe_route_scored(xn, router, self.correction, self.top, self.groups, self.keep_groups, ids, weights, **variant)
         elif M >= self.ROUTER_PRODUCT_FROM and self.E <= 1024:
             # many tokens: the logits as one matrix product (32-bit accumulation, the bias in its epilogue)
             logits = torch.empty((M, self.E), dtype=torch.float32, device=xn.device)
@@ -126,5 +140,8 @@ class MoEMLP(FeedForward):
                 K.moe_experts(xn, wgu, wd, ids, weights, residual, interleaved=True)
         else:
             K.moe_experts(xn, self.wgu.view(self.E, 2, self.F, self.d), wd, ids, weights, residual)
-        if self.shared is not None:
+        if self.shared_gated:
+            (y, _), = self.shared.forward_out(xn, step)
+            K.row_gate_add(residual, y, xn, self.shared_gate)
+        elif self.shared is not None:
             self.shared.forward(xn, residual, step)

@@ -51,6 +51,37 @@ class RMSNorm(Norm):
         return NormRequest(self.weight, self.eps) if self.weight is not None else None
 
 
+@register_norm("layer_norm")
+class LayerNorm(Norm):
+    """y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w: the mean is taken off, the variance is the mean of
+    the squared deviations, there is a weight and no bias; all in 32-bit.  ``forward_with`` norms the same rows with
+    a second norm of this kind in the same kernel (a layer whose two sublayers read norms of one stream)."""
+
+    def __init__(self, runtime: Runtime, size: int, eps: float, name: str):
+        self.runtime = runtime
+        self.size = size
+        self.eps = float(eps)
+        self.name = name
+        self.weight: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {"weight": ParamSpec((ParamSource(self.name, (self.size,)),), role="vector", init="ones")}
+
+    def forward(self, x: torch.Tensor, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n = x.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.size), dtype=out_dtype, device=x.device)
+        K.layer_norm(x, self.weight, out, self.eps, rows)
+        return out
+
+    def pairs_with(self, other: Norm) -> bool:
+        return isinstance(other, LayerNorm) and other.size == self.size and other.eps == self.eps
+
+    def forward_with(self, other: "LayerNorm", x: torch.Tensor, out_dtype: torch.dtype):
+        out = torch.empty((2, x.shape[0], self.size), dtype=out_dtype, device=x.device)
+        K.layer_norm(x, self.weight, out[0], self.eps, None, other.weight, out[1])
+        return out[0], out[1]
+
+
 @register_norm("none")
 class NoNorm(Norm):
     """The norm in front of a part that does not exist (a layer without a feed-forward)."""

@@ -158,6 +158,88 @@ class SelectiveStateSpace(_StateMixer):
         linear(yn, self.wo, residual, _out_mode)
 
 
+@register_mixer("shifted_decay_recurrence")
+class ShiftedDecayRecurrence(_StateMixer):
+    """Time mixing over a token's input h_t and its predecessor's h_{t-1} (zero before the sequence starts):
+
+        m_s = h_t + (h_{t-1} - h_t) * mu_s                for s in r, k, v, g, w (five learned vectors)
+        r, k, v = W_r m_r, W_k m_k, W_v m_v               (heads x head_dim each);   gate = silu(W_g m_g)
+        w = exp(-exp(W_w2 tanh(W_w1 m_w) + w0))           a decay a head and key channel, in (0, 1)
+        o_t = (S_{t-1} + diag(u) k_t v_t^T)^T r_t         per head; the bonus u weighs the current token alone
+        S_t = diag(w_t) S_{t-1} + k_t v_t^T
+        out = W_o (o / rms(o, per head) * norm * gate)
+
+    The per-sequence state is the last input the sequence was fed ([d]) and the heads' matrix states, float32, zero
+    for a fresh sequence.  The blends, the decay's logarithm from the second projection on, the decay, the state, the
+    sums and the head norm are 32-bit in every run; the projections and their activations take the compute dtype."""
+
+    MIXES = ("r", "k", "v", "g", "w")
+
+    def __init__(self, runtime: Runtime, hidden_size: int, num_heads: int, head_dim: int, decay_rank: int, norm_eps: float,
+                 names: Dict[str, str]):
+        """``names``: "mu" (prefix of the five blend vectors: + "r", "k", "v", "g", "w"), "r", "k", "v", "g", "o"
+        (matrices), "w1", "w2" (the decay's two projections), "w0" (its offset, a value a channel), "u" (the bonus,
+        [heads, head_dim]), "norm" (weight behind the head norm), "suffix"."""
+        if not (0 < head_dim <= 256) or num_heads <= 0 or decay_rank <= 0:
+            raise ValueError(f"head_dim {head_dim} must lie in (0, 256], heads {num_heads} and decay_rank {decay_rank} be positive")
+        self.runtime = runtime
+        self.d, self.H, self.n, self.rank = hidden_size, num_heads, head_dim, int(decay_rank)
+        self.eps = float(norm_eps)
+        self.names = names
+        self._shift_bytes = _aligned(4 * hidden_size)
+        self.mu = self.wr = self.wk = self.wv = self.wg = self.w1 = self.w2 = self.w0 = self.u = self.norm_w = self.wo = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        d, inner, n = self.d, self.H * self.n, self.names
+        sfx = n.get("suffix", ".weight")
+        specs = {"mu": ParamSpec(tuple(ParamSource(n["mu"] + s, (d,)) for s in self.MIXES), role="vector", init="normal")}
+        for key in ("r", "k", "v", "g"):
+            specs["w" + key] = ParamSpec((ParamSource(n[key] + sfx, (inner, d)),))
+        specs.update({
+            "w1": ParamSpec((ParamSource(n["w1"] + sfx, (self.rank, d)),)),
+            "w2": ParamSpec((ParamSource(n["w2"] + sfx, (inner, self.rank)),)),
+            "w0": ParamSpec((ParamSource(n["w0"], (inner,)),), role="vector", init="normal"),
+            "u": ParamSpec((ParamSource(n["u"], (self.H, self.n)),), role="vector", init="normal"),
+            "norm_w": ParamSpec((ParamSource(n["norm"], (inner,)),), role="vector", init="ones"),
+            "wo": ParamSpec((ParamSource(n["o"] + sfx, (d, inner)),)),
+        })
+        return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        if "mu" in tensors:          # five vectors one after another -> [5, d]
+            tensors = dict(tensors, mu=tensors["mu"].view(len(self.MIXES), self.d))
+        super().bind(tensors)
+
+    def state_need(self) -> StateNeed:
+        # the last input the sequence was fed, then the heads' matrix states
+        return StateNeed(self._shift_bytes + 4 * self.H * self.n * self.n)
+
+    def forward(self, xn, residual: torch.Tensor, step, cache, _out_mode=OUT_ADD_F32):
+        H, n, inner = self.H, self.n, self.H * self.n
+        M = xn.shape[0]
+        dt, dev = xn.dtype, xn.device
+        state = self._state(cache)
+        shift_state, scan_state = state[:, :self._shift_bytes], state[:, self._shift_bytes:]
+        mixes = torch.empty((len(self.MIXES), M, self.d), dtype=dt, device=dev)
+        K.token_shift_mix(xn, self.mu, step.positions, step.slot_of_token, step.cu_seqlens, shift_state, mixes)
+        proj = torch.empty((4, M, inner), dtype=dt, device=dev)          # r, k, v, g
+        for i, w in enumerate((self.wr, self.wk, self.wv, self.wg)):
+            linear(mixes[i], w, proj[i], OUT_SAME)
+        # the decay: the first projection's output and its tanh in 32-bit, the second projection's output (the decay's
+        # logarithm's logarithm, with its offset) in 32-bit; the scan forms exp(-exp(.)) itself
+        low = torch.empty((M, self.rank), dtype=torch.float32, device=dev)
+        linear(mixes[4], self.w1, low, OUT_F32)
+        low_t = torch.empty((M, self.rank), dtype=dt, device=dev)
+        K.tanh_cast(low, low_t)
+        wlog = torch.empty((M, inner), dtype=torch.float32, device=dev)
+        linear(low_t, self.w2, wlog, OUT_F32, self.w0)
+        o = torch.empty((M, inner), dtype=torch.float32, device=dev)
+        K.channel_decay_scan(proj[0], proj[1], proj[2], wlog, self.u, o, scan_state, step.cu_seqlens, step.seq_slots, H, n, n)
+        on = torch.empty((M, inner), dtype=dt, device=dev)
+        K.gated_norm(o, proj[3], self.norm_w, self.eps, on, groups=H, gate_act="silu", gate_first=False)
+        linear(on, self.wo, residual, _out_mode)
+
+
 @register_mixer("parallel_mixers")
 class ParallelMixers(Mixer):
     """Two mixers side by side on the same input: left_scale * left(h) + right_scale * right(h).  At most one of
@@ -205,7 +287,12 @@ class ParallelMixers(Mixer):
 
     def forward(self, xn, residual: torch.Tensor, step, cache):
         if self.scales != (1.0, 1.0):
-            raise K.KernelError("mixers side by side with factors other than 1 return their output through forward_out "
-                                "(a block that norms the sum); adding into the stream directly is not built")
+            # the two outputs as tensors of their own, then residual += a * left + b * right in one pass
+            terms = self.forward_out(xn, step, cache)
+            if len(terms) != 2:
+                raise K.KernelError("mixers side by side with factors: each must return one term")
+            (y0, s0), (y1, s1) = terms
+            K.scaled_add(residual, y0, s0, y1, s1)
+            return
         for m, view in zip((self.left, self.right), self._views(cache)):
             m.forward(xn, residual, step, view)

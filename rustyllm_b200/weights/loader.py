@@ -70,6 +70,9 @@ def runtime_dtype(role: str, file_dtype: torch.dtype, compute_dtype: torch.dtype
 
 def place_source(dest: torch.Tensor, ps: ParamSpec, index: int, tensor: torch.Tensor) -> None:
     """Copy source ``index`` of a parameter into its rows of ``dest`` (concatenated or interleaved)."""
+    if dest.dim() == 0:
+        dest.copy_(tensor.reshape(()))
+        return
     if ps.layout == "interleave":
         n = len(ps.sources)
         if any(s.shape != ps.sources[0].shape for s in ps.sources):
