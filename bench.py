@@ -19,8 +19,8 @@ HBM; no extra flush is needed.
 
     python bench.py --designs
 
-is another program under the same name: prompt and single-token throughput of the Mosurax, Mogutar and Forilorn
-designs beside the Llama decoder at two layer sizes of real models (``rustyllm_b200/bench_designs.py``), one JSON line a
+is another program under the same name: prompt and single-token throughput of the Mosurax, Mogutar, Forilorn and
+Besuzen designs beside the Llama decoder at two layer sizes of real models (``rustyllm_b200/bench_designs.py``), one JSON line a
 model and one with the ratios a size.  The headline workload above and its one line are untouched by it.
 """
 import argparse
@@ -126,7 +126,7 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="only the batch given (no batch 1 / 64 points)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="do not time the CPU baseline (vs_baseline stays null)")
     ap.add_argument("--designs", action="store_true",
-                    help="instead of the headline workload: prompt and single-token throughput of the Mosurax, Mogutar and Forilorn designs beside "
+                    help="instead of the headline workload: prompt and single-token throughput of the Mosurax, Mogutar, Forilorn and Besuzen designs beside "
                          "the Llama decoder at equal layer sizes (rustyllm_b200/bench_designs.py), a JSON line a model")
     args = ap.parse_args()
 

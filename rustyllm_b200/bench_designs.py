@@ -17,6 +17,12 @@ uses together with the shared one are as wide as the dense feed-forward), vocabu
                  mask and an output gate an element; one in four with attention through latents (queries 3/8 of the
                  width, at most 1,536; keys and values 1/4 of it, at most 512, plus a rotary key part of 64 for all heads, a window of 1,024, a gate
                  a head); dense gelu feed-forwards; a hashed pair table of 65,536 rows beside the embedding; tied head
+  besuzen        layers x += mixer(ln1(x)) + ff(ln2(x)) with layer norms; every second layer attention without rotation
+                 (a gate a head) beside a time mixer over the token and its predecessor with a matrix state a head and a
+                 decay a key channel (heads of 64, the model's width); the others rotated attention with an output gate an
+                 element whose values are blended with the first such layer's; feed-forwards in turn dense (gelu on the gate)
+                 and 16 experts in 4 groups (2 kept), 3 a token, softmax scores over all, with a gated shared expert
+``--besuzen-kernels`` times the Besuzen design's kernels alone, each beside the like kernel of the closest designs.
 ``--kernels`` times the Mogutar design's own kernels alone at the sizes of a layer (a JSON line a kernel, with the
 bytes it must move and their share of the measured copy bandwidth).
 Measured with CUDA events after warm-up: one prompt of ``prompt`` tokens as one step; then single-token steps of
@@ -39,7 +45,7 @@ SIZES = {
                   experts=16, top=3, expert_ff=3584, shared_ff=3584),
 }
 MAX_POSITIONS = 4096
-MODELS = ("llama", "mosurax-dense", "mosurax-moe", "mogutar", "forilorn")
+MODELS = ("llama", "mosurax-dense", "mosurax-moe", "mogutar", "forilorn", "besuzen")
 
 
 def llama_config(s: dict) -> dict:
@@ -91,6 +97,26 @@ def forilorn_config(s: dict, window: int = 1024) -> dict:
                "mlp": {"kind": "dense", "ff": s["ff"]}} for i in range(s["layers"])]
     return {"architecture": "Forilorn", "vocab": s["vocab"], "width": d, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
             "embedding": {"scale": d ** 0.5, "bigram": {"buckets": 65536, "mul_prev": 1000003, "mul_cur": 999983}}, "layers": layers}
+
+
+def besuzen_config(s: dict) -> dict:
+    d, H, G, hd = s["width"], s["heads"], s["kv_heads"], s["dim"]
+    att = {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5}
+    rotated = dict(att, rot={"base": 500000.0, "dims": hd}, v_mix=True)
+    right = {"heads": d // 64, "dim": 64, "decay_rank": 64}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    moe = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"], "groups": {"count": 4, "keep": 2}},
+           "expert": {"ff": s["expert_ff"]}, "shared": {"ff": s["shared_ff"]}}
+    layers = []
+    for i in range(s["layers"]):
+        mlp = moe if i % 2 else dense
+        if i % 2 == 0:
+            layers.append({"type": "parallel", "mlp": mlp,
+                           "mixer": {"left": dict(att), "right": dict(right), "left_scale": 0.6, "right_scale": 0.5}})
+        else:
+            layers.append({"type": "attention", "mixer": dict(rotated), "mlp": mlp})
+    return {"architecture": "Besuzen", "vocab": s["vocab"], "width": d, "norm": {"eps": 1e-6}, "embedding": {"scale": 3.0},
+            "logit_scale": 2.0, "layers": layers}
 
 
 def measure(config: dict, prompt: int, batches: List[int], context: int, steps: int, warmup: int) -> Dict[str, float]:
@@ -154,7 +180,7 @@ def run(sizes: List[str], prompt: int = 2048, batches=(8, 64), context: int = 10
         s = SIZES[name]
         got = {}
         for model in models:
-            cfg = llama_config(s) if model == "llama" else mogutar_config(s, window or 1024) if model == "mogutar" \
+            cfg = llama_config(s) if model == "llama" else besuzen_config(s) if model == "besuzen" else mogutar_config(s, window or 1024) if model == "mogutar" \
                 else forilorn_config(s, window or 1024) if model == "forilorn" else mosurax_config(s, model == "mosurax-moe", window or None)
             got[model] = measure(cfg, prompt, list(batches), context, steps, warmup)
             line = {"size": name, "model": model, "prompt_tokens": prompt, "context": context, "window": window or None,
@@ -446,6 +472,174 @@ def forilorn_kernel_times(sizes: List[str], prompt: int = 2048, batch: int = 64,
     return lines
 
 
+def besuzen_kernel_times(sizes: List[str], prompt: int = 2048, batch: int = 64, context: int = 1024, runs: int = 20) -> List[dict]:
+    """The Besuzen design's kernels alone, each beside the like kernel of the closest designs (Mosurax: gated attention,
+    rotation and cache write, RMS norm, gated product; Mogutar: recurrence, a pass over rows with per-sequence state, router
+    with groups), bfloat16, at a layer's sizes: ``prompt`` tokens of one sequence, and one token of each of ``batch``
+    sequences that hold ``context`` tokens with it.  A row gives the bytes the kernel must move and the operations it
+    must do, the time both would take at the measured copy bandwidth and matrix throughput, and the larger of the two
+    over the measured time (``of_roofline``)."""
+    import json as _json
+    import os
+    import torch
+    from . import kernels as K
+    from .cache.sequence_cache import KVNeed, SequenceCache
+    from .engine.step import StepState
+    peaks = {}
+    try:
+        with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")) as f:
+            peaks = _json.load(f)
+    except OSError:
+        pass
+    gbs, tflops = float(peaks.get("hbm_gbs", 6650.0)), float(peaks.get("bf16_tflops", 1590.0))
+    dev, bf = torch.device("cuda:0"), torch.bfloat16
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    rnd = lambda *shape: torch.randn(shape, dtype=torch.float32, device=dev)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(runs):
+            flush.zero_()                      # a buffer larger than L2 between runs
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return sorted(ts)[len(ts) // 2] * 1e3   # us
+
+    lines = []
+
+    def report(size, design, kernel, shape, us, nbytes, flops=0.0):
+        floor = max(nbytes / (gbs * 1e3), flops / (tflops * 1e6))        # us
+        line = {"size": size, "design": design, "kernel": kernel, "shape": shape, "us": round(us, 2), "gb": round(nbytes / 1e9, 4),
+                "gflop": round(flops / 1e9, 3), "floor_us": round(floor, 2), "of_roofline": round(floor / us, 3),
+                "bound": "bandwidth" if nbytes / (gbs * 1e3) >= flops / (tflops * 1e6) else "matrix"}
+        print(_json.dumps(line), flush=True)
+        lines.append(line)
+
+    for name in sizes:
+        s = SIZES[name]
+        d, H, G, hd, ff = s["width"], s["heads"], s["kv_heads"], s["dim"], s["ff"]
+        scale = hd ** -0.5
+        for what, B, held, cnt in (("prompt", 1, 0, prompt), ("single tokens", batch, context - 1, 1)):
+            M = B * cnt
+            shape = f"{what}: {M} tokens, {B} seq of {held + cnt}"
+            pairs = sum(p + 1 for p in range(held, held + cnt)) * B
+            cache = SequenceCache([KVNeed(G, hd)], [None], 64 * (-(-(held + cnt) // 64) + 1) * B, bf, dev, max_slots=B)
+            slots = [cache.alloc_slot() for _ in range(B)]
+            if held:
+                cache.prepare(slots, [held] * B); cache.commit(slots, [held] * B)
+            cache.prepare(slots, [cnt] * B)
+            st = StepState(M, B, i32([0] * M), i32([held + t for _ in range(B) for t in range(cnt)]),
+                           i32([sl for sl in slots for _ in range(cnt)]), i32([cnt * b for b in range(B + 1)]), i32(slots),
+                           i32([held + cnt] * B), i32([]), [cnt] * B, [held + cnt] * B, cnt, held + cnt, cnt == 1)
+            group, layer = cache.kv_entry(0)
+            kp, vp = group.k_pool(layer), group.v_pool(layer)
+            kp.normal_(); vp.normal_()
+            # ---- attention: a gate a head beside a gate an element ----
+            u = rnd(M, (2 * H + 2 * G) * hd).to(bf)
+            o = torch.empty((M, H * hd), dtype=bf, device=dev)
+            att_bytes = (held + cnt) * B * G * 2 * hd * 2 + 2 * M * H * hd * 2
+            for design, kw, extra in (("besuzen", dict(gate=u[:, (H + 2 * G) * hd:(H + 2 * G) * hd + H], gate_per_head=True), M * H * 2),
+                                      ("mosurax", dict(gate=u[:, (H + 2 * G) * hd:]), M * H * hd * 2)):
+                us = timed(lambda: K.attention(u, kp, vp, group.page_table, st, o, H, G, hd, scale, **kw))
+                report(name, design, "attention, " + ("gate a head" if "gate_per_head" in kw else "gate an element"),
+                       f"{shape}, {H} heads over {G} of {hd}", us, att_bytes + extra, 4.0 * pairs * H * hd)
+            # ---- rotation of neighbours, values blended, keys and values to pages; beside the half-split rotation ----
+            inv = torch.rand(hd // 2, dtype=torch.float32, device=dev)
+            u3 = rnd(M, (H + 2 * G) * hd).to(bf)
+            other, lam = rnd(M, G * hd).to(bf), torch.tensor(0.4, dtype=torch.float32, device=dev)
+            us = timed(lambda: K.rope_kv_write(u3, st.positions, st.slot_of_token, group.page_table, inv, H, G, hd, hd, True, kp, vp,
+                                               value_dim=hd, v_other=other, v_mix=lam))
+            report(name, "besuzen", "rotation of neighbours, values blended, keys and values to pages", f"{shape}, {H} + 2 x {G} heads of {hd}", us,
+                   M * (2 * H + 5 * G) * hd * 2)
+            us = timed(lambda: K.rope_kv_write(u3, st.positions, st.slot_of_token, group.page_table, inv, H, G, hd, hd, False, kp, vp, value_dim=hd))
+            report(name, "mosurax", "rotation, keys and values to pages", f"{shape}, {H} + 2 x {G} heads of {hd}", us, M * (2 * H + 4 * G) * hd * 2)
+            del cache
+            # ---- the recurrence with a decay a key channel beside the one with a decay a head ----
+            Hr, n = d // 64, 64
+            state = torch.zeros((B, 4 * Hr * n * n), dtype=torch.uint8, device=dev)
+            rkv = rnd(M, 3 * Hr * n).to(bf)
+            wlog, bonus = rnd(M, Hr * n) - 3.0, rnd(Hr, n)
+            o32 = torch.empty((M, Hr * n), dtype=torch.float32, device=dev)
+            us = timed(lambda: K.channel_decay_scan(rkv[:, :Hr * n], rkv[:, Hr * n:2 * Hr * n], rkv[:, 2 * Hr * n:], wlog, bonus, o32, state,
+                                                    st.cu_seqlens, st.seq_slots, Hr, n, n))
+            report(name, "besuzen", "recurrence, decay a key channel, bonus", f"{shape}, {Hr} heads of {n} x {n}", us,
+                   rkv.numel() * 2 + wlog.numel() * 4 + o32.numel() * 4 + 2 * state.numel(), 6.0 * M * Hr * n * n)
+            decay = torch.full((Hr,), 0.99, dtype=torch.float32, device=dev)
+            us = timed(lambda: K.linear_scan(rkv[:, :Hr * n], rkv[:, Hr * n:2 * Hr * n], rkv[:, 2 * Hr * n:], o32, state, st.cu_seqlens,
+                                             st.seq_slots, Hr, 1, n, n, decay, silu=True))
+            report(name, "mogutar", "recurrence, decay a head", f"{shape}, {Hr} heads of {n} x {n}", us,
+                   rkv.numel() * 2 + o32.numel() * 4 + 2 * state.numel(), 4.0 * M * Hr * n * n)
+            # ---- the blends with the previous token beside the short convolution (a pass over rows with per-sequence state) ----
+            h = rnd(M, d).to(bf)
+            mu = torch.rand(5, d, dtype=torch.float32, device=dev)
+            sstate = torch.zeros((B, 4 * d), dtype=torch.uint8, device=dev)
+            mixes = torch.empty((5, M, d), dtype=bf, device=dev)
+            us = timed(lambda: K.token_shift_mix(h, mu, st.positions, st.slot_of_token, st.cu_seqlens, sstate, mixes))
+            report(name, "besuzen", "five blends with the previous token + state", f"{shape}, width {d}", us, 6 * M * d * 2 + 2 * sstate.numel())
+            cstate = torch.zeros((B, 4 * 3 * d), dtype=torch.uint8, device=dev)
+            wconv = rnd(d, 4)
+            cout = torch.empty((M, d), dtype=bf, device=dev)
+            us = timed(lambda: (K.short_conv(h, wconv, None, True, st.slot_of_token, cstate, cout), K.short_conv_state(h, 4, st.cu_seqlens, st.seq_slots, cstate)))
+            report(name, "mogutar", "short convolution + state", f"{shape}, {d} channels, 4 taps", us, 2 * M * d * 2 + 2 * cstate.numel())
+            # ---- the head norm with the gate behind the recurrence (the kernel is Mogutar's) ----
+            gate = rnd(M, Hr * n).to(bf)
+            ones = torch.ones(Hr * n, dtype=torch.float32, device=dev)
+            on = torch.empty((M, Hr * n), dtype=bf, device=dev)
+            us = timed(lambda: K.gated_norm(o32, gate, ones, 1e-6, on, groups=Hr, gate_act="silu", gate_first=False))
+            report(name, "besuzen", "unit heads, weight, silu gate", f"{shape}, {Hr} heads of {n}", us, M * Hr * n * (4 + 2 + 2))
+            us = timed(lambda: K.gated_norm(o32, gate, ones, 1e-6, on, groups=8, gate_act="silu", gate_first=True))
+            report(name, "mogutar", "gate, norm in 8 parts, weight", f"{shape}, width {Hr * n}", us, M * Hr * n * (4 + 2 + 2))
+            # ---- both layer norms of a layer in one kernel beside two RMS norms ----
+            x = rnd(M, d)
+            w0, w1 = torch.ones(d, dtype=torch.float32, device=dev), torch.ones(d, dtype=torch.float32, device=dev)
+            pair = torch.empty((2, M, d), dtype=bf, device=dev)
+            us = timed(lambda: K.layer_norm(x, w0, pair[0], 1e-6, None, w1, pair[1]))
+            report(name, "besuzen", "two layer norms of one stream", f"{shape}, width {d}", us, M * d * (4 + 2 + 2))
+            us = timed(lambda: (K.rmsnorm(x, w0, pair[0], 1e-6), K.rmsnorm(x, w1, pair[1], 1e-6)))
+            report(name, "mosurax", "two RMS norms", f"{shape}, width {d}", us, M * d * (4 + 4 + 2 + 2))
+            # ---- the joins ----
+            y0, y1 = rnd(M, d), rnd(M, d)
+            us = timed(lambda: K.scaled_add(x, y0, 0.6, y1, 0.5))
+            report(name, "besuzen", "stream += a * left + b * right", f"{shape}, width {d}", us, M * d * 16)
+            xb = torch.empty((M, d), dtype=bf, device=dev)
+            us = timed(lambda: K.norm_add(x, y0, 0.6, y1, 0.5, w0, 1e-6, xb))
+            report(name, "mogutar", "stream += norm(a * left + b * right) w", f"{shape}, width {d}", us, M * d * 18)
+            gvec = rnd(d).to(bf)
+            us = timed(lambda: K.row_gate_add(x, y0, h, gvec))
+            report(name, "besuzen", "stream += sigmoid(h . g) * shared", f"{shape}, width {d}", us, M * d * 14)
+            # ---- routers ----
+            E, top = s["experts"], s["top"]
+            wr = (rnd(E, d) * d ** -0.5).to(bf)
+            ids = torch.empty((M, top), dtype=torch.int32, device=dev)
+            wts = torch.empty((M, top), dtype=torch.float32, device=dev)
+            if M < 128:
+                us = timed(lambda: K.moe_route_scored(h, wr, None, top, 4, 2, ids, wts, softmax_all=True, group_top=1, renorm=True))
+                report(name, "besuzen", "router, softmax over all, groups by their best", f"{shape}, {E} experts", us, M * d * 2 + E * d * 2)
+                us = timed(lambda: K.moe_route_sigmoid(h, wr, None, top, 4, 2, ids, wts))
+                report(name, "mogutar", "router, sigmoid scores, groups by their two best", f"{shape}, {E} experts", us, M * d * 2 + E * d * 2)
+            else:
+                logits = rnd(M, E)
+                us = timed(lambda: K.moe_select_scored(logits, None, top, 4, 2, ids, wts, softmax_all=True, group_top=1, renorm=True))
+                report(name, "besuzen", "choice from logits, softmax over all", f"{shape}, {E} experts", us, M * E * 4 + M * top * 8)
+                us = timed(lambda: K.moe_select_sigmoid(logits, None, top, 4, 2, ids, wts))
+                report(name, "mogutar", "choice from logits, sigmoid scores", f"{shape}, {E} experts", us, M * E * 4 + M * top * 8)
+            # ---- the feed-forward's first product with its activation in the epilogue ----
+            w2 = (rnd(2 * ff, d) * d ** -0.5).to(bf)
+            hh = torch.empty((M, ff), dtype=bf, device=dev)
+            for design, mode in (("besuzen", K.OUT_GEGLU), ("mosurax", K.OUT_SWIGLU)):
+                us = timed(lambda: K.gemm_tc(h, w2, hh, mode))
+                report(name, design, "gate-up product, " + ("gelu" if mode == K.OUT_GEGLU else "silu") + " on the gate in the epilogue",
+                       f"{shape}, {d} -> 2 x {ff}", us, w2.numel() * 2 + M * (d + ff) * 2, 4.0 * M * d * ff)
+    K.check_device_errors()
+    return lines
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--size", action="append", choices=sorted(SIZES), help="default: all")
@@ -453,6 +647,8 @@ def main(argv=None) -> int:
     ap.add_argument("--kernels", action="store_true", help="time the Mogutar design's own kernels alone instead")
     ap.add_argument("--forilorn-kernels", action="store_true",
                     help="time the Forilorn design's kernels alone, each beside the like kernel of the Mosurax design, instead")
+    ap.add_argument("--besuzen-kernels", action="store_true",
+                    help="time the Besuzen design's kernels alone, each beside the like kernel of the Mosurax or Mogutar design, instead")
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--batch", type=int, action="append", help="default: 8 and 64")
@@ -462,6 +658,9 @@ def main(argv=None) -> int:
     a = ap.parse_args(argv)
     if a.forilorn_kernels:
         forilorn_kernel_times(a.size or sorted(SIZES), a.prompt, max(a.batch or (64,)), a.context, a.window or 1024)
+        return 0
+    if a.besuzen_kernels:
+        besuzen_kernel_times(a.size or sorted(SIZES), a.prompt, max(a.batch or (64,)), a.context)
         return 0
     if a.kernels:
         kernel_times(a.size or sorted(SIZES), a.prompt, max(a.batch or (64,)))

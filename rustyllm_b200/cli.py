@@ -280,7 +280,11 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool, layer_index: int = 0)
     x = torch.randn(1, d, device=dev)
     xn = torch.empty(1, d, device=dev, dtype=dt)
     rows = []
-    rows.append(("attn_norm.rms", timed(lambda: K.rmsnorm(x, blk.mixer_norm.weight, xn, blk.mixer_norm.eps)), d * 4))
+    from .parts.norm import LayerNorm
+    if isinstance(blk.mixer_norm, LayerNorm):
+        rows.append(("attn_norm.layer", timed(lambda: K.layer_norm(x, blk.mixer_norm.weight, xn, blk.mixer_norm.eps)), d * 4))
+    else:
+        rows.append(("attn_norm.rms", timed(lambda: K.rmsnorm(x, blk.mixer_norm.weight, xn, blk.mixer_norm.eps)), d * 4))
 
     def product_rows(tag, w_in, b_in, w_out, b_out):
         """The input and output products of a mixer."""
@@ -300,7 +304,7 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool, layer_index: int = 0)
     if hasattr(att, "wqkv"):
         qkv = product_rows("attn_qkv", att.wqkv, att.bqkv, att.wo, att.bo)
     for m, tag in ((other, "mixer2_in"), (None if hasattr(att, "wqkv") else att, "mixer_in")):
-        w_in = next((getattr(m, n) for n in ("w_in", "wqkvg") if m is not None and getattr(m, n, None) is not None), None)
+        w_in = next((getattr(m, n) for n in ("w_in", "wqkvg", "wr") if m is not None and getattr(m, n, None) is not None), None)
         if w_in is not None:
             product_rows(tag, w_in, None, m.wo, None)
     from .parts.mlp import GatedMLP
@@ -311,7 +315,10 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool, layer_index: int = 0)
         xf = xn.to(ff.wgu.dtype)
         rows.append((f"{tag}_gate_up.fused", timed(lambda: linear(xf, ff.wgu, gu, OUT_SAME, ff.bgu)), ff.wgu.numel() * ff.wgu.element_size()))
         h = torch.empty(1, ff.I, device=dev, dtype=gu.dtype)
-        rows.append((f"{tag}_activation.silu_mul", timed(lambda: K.swiglu(gu, h, interleaved=ff.interleaved)), 3 * ff.I * esz))
+        if getattr(ff, "activation", "silu") == "gelu_tanh":
+            rows.append((f"{tag}_activation.gelu_mul", timed(lambda: K.geglu(gu, h, interleaved=ff.interleaved)), 3 * ff.I * esz))
+        else:
+            rows.append((f"{tag}_activation.silu_mul", timed(lambda: K.swiglu(gu, h, interleaved=ff.interleaved)), 3 * ff.I * esz))
         rows.append((f"{tag}_down", timed(lambda: linear(h, ff.wdown, x, OUT_ADD_F32, ff.bdown)), ff.wdown.numel() * ff.wdown.element_size()))
 
     from .parts.mlp import DenseMLP
@@ -324,7 +331,10 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool, layer_index: int = 0)
         xe = xn.to(ff.router.dtype)
         ids = torch.empty((1, ff.top), dtype=torch.int32, device=dev)
         wts = torch.empty((1, ff.top), dtype=torch.float32, device=dev)
-        if getattr(ff, "scoring", "softmax") == "sigmoid":
+        if getattr(ff, "scoring", "softmax") == "softmax_all":
+            rows.append(("ffn_router", timed(lambda: K.moe_route_scored(xe, ff.router, None, ff.top, ff.groups, ff.keep_groups, ids, wts,
+                                                                        softmax_all=True, group_top=1, renorm=True)), ff.router.numel() * esz))
+        elif getattr(ff, "scoring", "softmax") == "sigmoid":
             rows.append(("ffn_router", timed(lambda: K.moe_route_sigmoid(xe, ff.router, ff.correction, ff.top, ff.groups, ff.keep_groups, ids, wts)),
                          ff.router.numel() * esz))
         else:
@@ -360,7 +370,7 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool, layer_index: int = 0)
         t = timed(lambda: K.attention(q, group.k_pool(layer), group.v_pool(layer), group.page_table, st, o, att.H, att.G, att.hd, att.scale,
                                       att.window or 0, value_dim=att.vd, sink=getattr(att, "sink", False), gate=gate,
                                       softcap=getattr(att, "softcap", 0.0), keep_first=getattr(att, "keep_first", 0),
-                                      chunk=getattr(att, "chunk", None) or 0))
+                                      chunk=getattr(att, "chunk", None) or 0, gate_per_head=getattr(att, "gate_per_head", False)))
         seen = min(ctx + 1, att.window) if att.window else ctx % att.chunk + 1 if getattr(att, "chunk", None) else ctx + 1
         rows.append((f"attn_scan.ctx{ctx}", t, seen * att.G * (att.hd + att.vd) * esz))
         eng.free_slot(s)

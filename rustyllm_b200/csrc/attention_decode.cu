@@ -206,6 +206,7 @@ struct DecFinish {
   // in front of a window
   float softcap;
   int keep_first;
+  int gate_head;      // 0: the gate holds a number an output element; HD: one number a head (gate[b, h])
 };
 
 __device__ __forceinline__ float dec_finish(float O, float L, float M, const DecFinish& f, int b, int col) {
@@ -216,7 +217,7 @@ __device__ __forceinline__ float dec_finish(float O, float L, float M, const Dec
     L = L * w + exp2f(-M2);
   }
   float o = L > 0.f ? O / L : 0.f;
-  if (f.gate) o *= 1.0f / (1.0f + expf(-__bfloat162float(f.gate[(size_t)b * f.ldg + col])));
+  if (f.gate) o *= 1.0f / (1.0f + expf(-__bfloat162float(f.gate[(size_t)b * f.ldg + (f.gate_head ? col / f.gate_head : col)])));
   return o;
 }
 
@@ -681,15 +682,16 @@ extern "C" int rl_attention_decode_order(const int* seq_slots, const int* kv_len
 // sigmoid(gate[b, h*head_dim + i]) before it is stored.  softcap > 0: a score s (scale included) becomes
 // softcap * tanh(s / softcap).  keep_first > 0 (with a window): positions [0, keep_first) stay visible.
 // window < 0: a chunked mask with blocks of -window positions (the query sees its own block up to itself).
-extern "C" int rl_attention_decode_masked(const void* q, int ldq, const void* k_pool, const void* v_pool,
-                                          const int* page_table, int max_pages, const int* seq_slots, const int* kv_lens,
-                                          void* out, int ldo, float* scratch, const int* plan, int num_seqs, int num_heads,
-                                          int num_kv_heads, int head_dim, float scale, int window, int num_splits,
-                                          int sink, const void* gate, int ldg, float softcap, int keep_first,
-                                          cudaStream_t stream) {
-  RL_REQUIRE(gate == nullptr || ldg >= num_heads * head_dim, "rl_attention_decode: the gate's row stride is too small");
+// gate_per_head != 0: the gate is [num_seqs, ldg] with one number a head, sigmoid(gate[b, h]) on all of head h's output.
+extern "C" int rl_attention_decode_headgate(const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                            const int* page_table, int max_pages, const int* seq_slots, const int* kv_lens,
+                                            void* out, int ldo, float* scratch, const int* plan, int num_seqs, int num_heads,
+                                            int num_kv_heads, int head_dim, float scale, int window, int num_splits,
+                                            int sink, const void* gate, int ldg, float softcap, int keep_first, int gate_per_head,
+                                            cudaStream_t stream) {
+  RL_REQUIRE(gate == nullptr || ldg >= (gate_per_head ? num_heads : num_heads * head_dim), "rl_attention_decode: the gate's row stride is too small");
   RL_REQUIRE(softcap >= 0.f && keep_first >= 0, "rl_attention_decode: negative soft cap or number of kept first tokens");
-  const DecFinish fin = {sink, (const __nv_bfloat16*)gate, ldg, softcap, window > 0 ? keep_first : 0};
+  const DecFinish fin = {sink, (const __nv_bfloat16*)gate, ldg, softcap, window > 0 ? keep_first : 0, gate_per_head ? head_dim : 0};
   RL_REQUIRE(rl_attention_decode_supported(num_heads, num_kv_heads, head_dim),
              "rl_attention_decode: unsupported shape (heads %d, KV heads %d, head_dim %d): needs head_dim 64 or 128 "
              "and at most 16 heads per KV head", num_heads, num_kv_heads, head_dim);
@@ -712,6 +714,17 @@ extern "C" int rl_attention_decode_masked(const void* q, int ldq, const void* k_
                              part_ml, plan, num_seqs, num_heads, num_kv_heads, scale, window, num_splits, fin, stream);
   return launch_decode<128>(q, ldq, k_pool, v_pool, page_table, max_pages, seq_slots, kv_lens, out, ldo, part_o,
                             part_ml, plan, num_seqs, num_heads, num_kv_heads, scale, window, num_splits, fin, stream);
+}
+
+extern "C" int rl_attention_decode_masked(const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                          const int* page_table, int max_pages, const int* seq_slots, const int* kv_lens,
+                                          void* out, int ldo, float* scratch, const int* plan, int num_seqs, int num_heads,
+                                          int num_kv_heads, int head_dim, float scale, int window, int num_splits,
+                                          int sink, const void* gate, int ldg, float softcap, int keep_first,
+                                          cudaStream_t stream) {
+  return rl_attention_decode_headgate(q, ldq, k_pool, v_pool, page_table, max_pages, seq_slots, kv_lens, out, ldo, scratch, plan,
+                                      num_seqs, num_heads, num_kv_heads, head_dim, scale, window, num_splits, sink, gate, ldg, softcap,
+                                      keep_first, 0, stream);
 }
 
 extern "C" int rl_attention_decode_gated(const void* q, int ldq, const void* k_pool, const void* v_pool,

@@ -196,7 +196,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ kv_lens, int num_seqs, __nv_bfloat16* __restrict__ out, int ldo,
                             int H, int G, float scale_log2e, int window, int* __restrict__ err,
                             const int* __restrict__ tile_order, int sink, const __nv_bfloat16* __restrict__ gate, int ldg,
-                            float cap_in, float cap_out, int keep_first, int chunk) {
+                            float cap_in, float cap_out, int keep_first, int chunk, int gate_per_head) {
   extern __shared__ uint8_t fa_smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)fa_smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* q_tile = smem;                                   // [2 halves][128 x 64]
@@ -570,9 +570,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // sink: one more term in the denominator, of score 0 and without a value; O and the sums are in
         // units of exp2(-m_fin), so the term is exp2(0 - m_fin) (a row without keys: 1 / inf = 0)
         const float l_all = sink ? l_row + fa_exp2(-m_fin) : l_row;
-        const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+        float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
         __nv_bfloat16* orow = out + (size_t)(row0 + qt0 + r) * ldo + (size_t)h * HD + grp * OC;
-        const __nv_bfloat16* grow = gate ? gate + (size_t)(row0 + qt0 + r) * ldg + (size_t)h * HD + grp * OC : nullptr;
+        const __nv_bfloat16* grow = (gate && !gate_per_head) ? gate + (size_t)(row0 + qt0 + r) * ldg + (size_t)h * HD + grp * OC : nullptr;
+        if (gate && gate_per_head && r < rows_here)      // one number a head: sigmoid(gate[m, h]) on the whole row, in 32-bit
+          inv *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)(row0 + qt0 + r) * ldg + h])));
 #pragma unroll 1
         for (int c = 0; c < OC / 16; ++c) {
           uint32_t v[16];
@@ -581,14 +583,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           if (r < rows_here) {
             uint32_t pk[8];
             uint32_t gk[8];
-            if (gate) {        // output gate: 16 bf16 of this row, 16-byte aligned (checked on the host)
+            if (grow) {        // output gate: 16 bf16 of this row, 16-byte aligned (checked on the host)
               const uint4 g0 = *reinterpret_cast<const uint4*>(grow + c * 16), g1 = *reinterpret_cast<const uint4*>(grow + c * 16 + 8);
               gk[0] = g0.x; gk[1] = g0.y; gk[2] = g0.z; gk[3] = g0.w; gk[4] = g1.x; gk[5] = g1.y; gk[6] = g1.z; gk[7] = g1.w;
             }
 #pragma unroll
             for (int j = 0; j < 16; j += 2) {
               float a = __uint_as_float(v[j]) * inv, b = __uint_as_float(v[j + 1]) * inv;
-              if (gate) {      // times sigmoid(gate) in 32-bit, before the one rounding to bf16
+              if (grow) {      // times sigmoid(gate) in 32-bit, before the one rounding to bf16
                 const float2 gg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gk[j >> 1]));
                 a *= 1.0f / (1.0f + expf(-gg.x)); b *= 1.0f / (1.0f + expf(-gg.y));
               }
@@ -658,18 +660,20 @@ extern "C" int rl_attention_prefill_tc_supported(int num_heads, int num_kv_heads
 // softcap > 0: a score s (scale included) becomes softcap * tanh(s / softcap).  keep_first > 0 (with a window):
 // positions [0, keep_first) stay visible behind the window.  chunk > 0 (instead of a window): a query at position p sees
 // positions [p - p % chunk, p], the positions of its own block counted from the sequence's start.
-extern "C" int rl_attention_prefill_tc_shaped(const void* q, int ldq, const void* k_pool, const void* v_pool, int num_pages,
-                                              const int* page_table, int max_pages, const int* cu_seqlens,
-                                              const int* seq_slots, const int* kv_lens, int num_seqs, int num_tiles,
-                                              int num_tokens, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
-                                              float scale, int window, int* err, const int* tile_order, int sink,
-                                              const void* gate, int ldg, float softcap, int keep_first, int chunk,
-                                              cudaStream_t stream) {
+// gate_per_head != 0: the gate is bf16 [M, ldg] with one number a head (no alignment rule): sigmoid(gate[m, h]) on all of
+// head h's output.
+extern "C" int rl_attention_prefill_tc_headgate(const void* q, int ldq, const void* k_pool, const void* v_pool, int num_pages,
+                                                const int* page_table, int max_pages, const int* cu_seqlens,
+                                                const int* seq_slots, const int* kv_lens, int num_seqs, int num_tiles,
+                                                int num_tokens, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
+                                                float scale, int window, int* err, const int* tile_order, int sink,
+                                                const void* gate, int ldg, float softcap, int keep_first, int chunk, int gate_per_head,
+                                                cudaStream_t stream) {
   RL_REQUIRE(chunk >= 0 && !(chunk > 0 && window > 0), "rl_attention_prefill_tc: a chunked mask and a window exclude one another");
   RL_REQUIRE(softcap >= 0.f && keep_first >= 0 && scale > 0.f, "rl_attention_prefill_tc: negative soft cap or number of kept first tokens, or a scale that is not positive");
   const float cap_in = softcap > 0.f ? scale / softcap : 0.f, cap_out = softcap > 0.f ? softcap / scale : 0.f;
   if (window <= 0) keep_first = 0;
-  RL_REQUIRE(gate == nullptr || (ldg >= num_heads * head_dim && ldg % 8 == 0 && ((uintptr_t)gate & 15) == 0),
+  RL_REQUIRE(gate == nullptr || (gate_per_head && ldg >= num_heads) || (!gate_per_head && ldg >= num_heads * head_dim && ldg % 8 == 0 && ((uintptr_t)gate & 15) == 0),
              "rl_attention_prefill_tc: the gate must be 16-byte aligned with a row stride that is a multiple of 8 and holds all heads");
   RL_REQUIRE(rl_attention_prefill_tc_supported(num_heads, num_kv_heads, head_dim),
              "rl_attention_prefill_tc: unsupported shape (heads %d, KV heads %d, head_dim %d): needs head_dim 64 or 128",
@@ -701,16 +705,28 @@ extern "C" int rl_attention_prefill_tc_shaped(const void* q, int ldq, const void
       ? rl_launch_pdl(attention_prefill_tc_kernel<128>, dim3(num_heads, num_tiles), dim3(FA_THREADS), (size_t)FaSizes<128>::SMEM, stream,
                       mq, mk, mv, page_table, max_pages, cu_seqlens, seq_slots, kv_lens, num_seqs,
                       (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err, tile_order,
-                      sink, (const __nv_bfloat16*)gate, ldg, cap_in, cap_out, keep_first, chunk)
+                      sink, (const __nv_bfloat16*)gate, ldg, cap_in, cap_out, keep_first, chunk, gate_per_head)
       : rl_launch_pdl(attention_prefill_tc_kernel<64>, dim3(num_heads, num_tiles), dim3(FA_THREADS), (size_t)FaSizes<64>::SMEM, stream,
                       mq, mk, mv, page_table, max_pages, cu_seqlens, seq_slots, kv_lens, num_seqs,
                       (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err, tile_order,
-                      sink, (const __nv_bfloat16*)gate, ldg, cap_in, cap_out, keep_first, chunk);
+                      sink, (const __nv_bfloat16*)gate, ldg, cap_in, cap_out, keep_first, chunk, gate_per_head);
   if (e != cudaSuccess) {
     rl_set_error("rl_attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
     return RL_ERR_CUDA;
   }
   return RL_OK;
+}
+
+extern "C" int rl_attention_prefill_tc_shaped(const void* q, int ldq, const void* k_pool, const void* v_pool, int num_pages,
+                                              const int* page_table, int max_pages, const int* cu_seqlens,
+                                              const int* seq_slots, const int* kv_lens, int num_seqs, int num_tiles,
+                                              int num_tokens, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
+                                              float scale, int window, int* err, const int* tile_order, int sink,
+                                              const void* gate, int ldg, float softcap, int keep_first, int chunk,
+                                              cudaStream_t stream) {
+  return rl_attention_prefill_tc_headgate(q, ldq, k_pool, v_pool, num_pages, page_table, max_pages, cu_seqlens, seq_slots, kv_lens,
+                                          num_seqs, num_tiles, num_tokens, out, ldo, num_heads, num_kv_heads, head_dim, scale, window,
+                                          err, tile_order, sink, gate, ldg, softcap, keep_first, chunk, 0, stream);
 }
 
 extern "C" int rl_attention_prefill_tc_masked(const void* q, int ldq, const void* k_pool, const void* v_pool, int num_pages,

@@ -139,6 +139,70 @@ rope_kv_write_bf16_half_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const in
   }
 }
 
+// Fast path for neighbouring pairs: bf16, rotary width, head size and value size multiples of 8, 16-byte aligned rows.
+// A thread takes eight consecutive elements (one 16-byte load): four pairs (2i, 2i + 1) that it rotates by itself
+// where they lie inside the rotary width, or eight value elements, which it blends with another layer's values of
+// the same token where those are given, v <- (1 - lam) v + lam v_other in 32-bit.  The token's sines and cosines
+// are computed once a CTA.
+__global__ void __launch_bounds__(ROPE_THREADS)
+rope_kv_write_bf16_pairs_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const int* __restrict__ positions,
+                                const int* __restrict__ slot_of_token, const int* __restrict__ page_table, int max_pages,
+                                const float* __restrict__ inv_freq, int H, int G, int hd, int vd, int rot,
+                                __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool,
+                                const __nv_bfloat16* __restrict__ v_other, int ld_other, const float* __restrict__ v_mix) {
+  __shared__ float2 cs[128];                              // (cos, sin) of the token's rot / 2 <= 128 angles
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  const int m = blockIdx.x;
+  const int pos = positions[m];
+  __nv_bfloat16* row = qkv + (size_t)m * ld;
+  const int page = page_table[(size_t)slot_of_token[m] * max_pages + pos / RL_PAGE];
+  const size_t dst_k = ((size_t)page * G) * RL_PAGE * hd + (size_t)(pos % RL_PAGE) * hd;
+  const size_t dst_v = ((size_t)page * G) * RL_PAGE * vd + (size_t)(pos % RL_PAGE) * vd;
+  for (int i = threadIdx.x; i < rot / 2; i += ROPE_THREADS) {
+    float sn, c;
+    sincosf((float)pos * inv_freq[i], &sn, &c);
+    cs[i] = make_float2(c, sn);
+  }
+  __syncthreads();
+  const int qk8 = (H + G) * hd / 8, v8 = G * vd / 8;
+  const float lam = v_other ? *v_mix : 0.f;
+  for (int idx = threadIdx.x; idx < qk8 + v8; idx += ROPE_THREADS) {
+    if (idx < qk8) {
+      const int e = idx * 8, hs = e / hd, i = e % hd;     // head slot [0, H) q, [H, H + G) k; first element within the head
+      __nv_bfloat16* x = row + e;
+      uint4 v = *reinterpret_cast<const uint4*>(x);
+      if (i < rot) {
+        __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 a = __bfloat1622float2(p[k]);
+          const float2 t = cs[i / 2 + k];
+          p[k] = __floats2bfloat162_rn(a.x * t.x - a.y * t.y, a.y * t.x + a.x * t.y);
+        }
+        if (hs < H) *reinterpret_cast<uint4*>(x) = v;
+      }
+      if (hs >= H) *reinterpret_cast<uint4*>(k_pool + dst_k + (size_t)(hs - H) * RL_PAGE * hd + i) = v;
+    } else {
+      const int e = (idx - qk8) * 8, g = e / vd, i = e % vd;
+      __nv_bfloat16* x = row + (size_t)(H + G) * hd + e;
+      uint4 v = *reinterpret_cast<const uint4*>(x);
+      if (v_other) {
+        const uint4 o = *reinterpret_cast<const uint4*>(v_other + (size_t)m * ld_other + e);
+        __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+        const __nv_bfloat162* q = reinterpret_cast<const __nv_bfloat162*>(&o);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 a = __bfloat1622float2(p[k]), b = __bfloat1622float2(q[k]);
+          p[k] = __floats2bfloat162_rn((1.0f - lam) * a.x + lam * b.x, (1.0f - lam) * a.y + lam * b.y);
+        }
+        *reinterpret_cast<uint4*>(x) = v;
+      }
+      *reinterpret_cast<uint4*>(v_pool + dst_v + (size_t)g * RL_PAGE * vd + i) = v;
+    }
+  }
+}
+
 // No rotation at all (rotary width 0): keys and values go to their pages as they are, 16 bytes a thread;
 // the queries stay where they are.  One CTA a token; any dtype (bytes are copied).
 __global__ void __launch_bounds__(ROPE_THREADS)
@@ -199,6 +263,12 @@ extern "C" int rl_rope_kv_write_mixed(void* qkv, int dtype, int ld, const int* p
                   threads, 0, stream, (__nv_bfloat16*)qkv, ld, positions,
                   slot_of_token, page_table, max_pages, inv_freq, num_heads, num_kv_heads, head_dim,
                   (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool);
+  else if (dtype == RL_BF16 && write_cache && interleaved && rotary_dim > 0 && rotary_dim % 8 == 0 && head_dim % 8 == 0 && value_dim % 8 == 0 &&
+           ld % 8 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0 &&
+           (v_other == nullptr || (ld_other % 8 == 0 && ((uintptr_t)v_other & 15) == 0)))
+    rl_launch_pdl(rope_kv_write_bf16_pairs_kernel, dim3(num_tokens), threads, 0, stream, (__nv_bfloat16*)qkv, ld, positions, slot_of_token,
+                  page_table, max_pages, inv_freq, num_heads, num_kv_heads, head_dim, value_dim, rotary_dim, (__nv_bfloat16*)k_pool,
+                  (__nv_bfloat16*)v_pool, (const __nv_bfloat16*)v_other, ld_other, v_mix);
   else if (dtype == RL_F32)
     rl_launch_pdl(rope_kv_write_kernel<float>, grid, threads, 0, stream,
         (float*)qkv, ld, positions, slot_of_token, page_table, max_pages, inv_freq, num_heads,

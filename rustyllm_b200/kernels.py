@@ -145,6 +145,12 @@ _SIGNATURES = {
     "rl_attention_prefill_tc_shaped": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                                        _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
                                        _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_float, _c_int, _c_int, _c_void_p],
+    "rl_attention_decode_headgate": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                     _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
+                                     _c_int, _c_void_p, _c_int, _c_float, _c_int, _c_int, _c_void_p],
+    "rl_attention_prefill_tc_headgate": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                                         _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                         _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void_p],
     "rl_attention_decode_plan": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_attention_decode_order": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_attention_decode_places": [_c_int],
@@ -512,9 +518,10 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_of_token: tor
     is the width of a value head.  ``v_other`` [M, G*vd] (a view is fine) with ``v_mix`` (a float32 scalar on the
     device): the values become (1 - v_mix) v + v_mix v_other, in 32-bit, before they are cached."""
     vd = head_dim if value_dim is None else value_dim
-    _need(qkv, "qkv"); _need(positions, "positions", torch.int32)
+    _need(qkv, "qkv", contiguous=False); _need(positions, "positions", torch.int32)
     _need(inv_freq, "inv_freq", torch.float32)
     M = qkv.shape[0]
+    assert qkv.stride(1) == 1 and (M == 1 or qkv.stride(0) >= qkv.shape[1])
     if k_pool is not None:
         _need(k_pool, "k_pool", qkv.dtype); _need(v_pool, "v_pool", qkv.dtype)
         _need(slot_of_token, "slot_of_token", torch.int32); _need(page_table, "page_table", torch.int32)
@@ -1346,7 +1353,8 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
                      num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
                      num_splits: Optional[int] = None, scratch: Optional[torch.Tensor] = None,
                      plan: Optional[torch.Tensor] = None, cluster: bool = False, sink: bool = False,
-                     gate: Optional[torch.Tensor] = None, softcap: float = 0.0, keep_first: int = 0) -> None:
+                     gate: Optional[torch.Tensor] = None, softcap: float = 0.0, keep_first: int = 0,
+                     gate_per_head: bool = False) -> None:
     """One token per sequence over the bf16 cache, split over the context (tensor cores).
     q: [B, >= H*hd] bf16 (a view into the qkv buffer is fine); out: [B, H*hd] bf16.
     ``num_splits``: chunks per sequence; with a ``plan`` (from ``decode_plan`` with the
@@ -1376,12 +1384,12 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
         _need(plan, "plan", torch.int32)
         assert plan.numel() >= 4 * B * num_splits + 2 * B
     ldq = q.stride(0) if B > 1 else max(q.stride(0), num_heads * head_dim)
-    gptr, ldg = _gate_args(gate, B, num_heads * head_dim, 2)
-    _check(library().rl_attention_decode_masked(
+    gptr, ldg = _gate_args(gate, B, num_heads if gate_per_head else num_heads * head_dim, 2)
+    _check(library().rl_attention_decode_headgate(
         q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         seq_slots.data_ptr(), kv_lens.data_ptr(), out.data_ptr(), out.stride(0), _ptr(scratch), _ptr(plan), B,
         num_heads, num_kv_heads, head_dim, float(scale), int(window), int(num_splits), int(bool(sink)), gptr, ldg,
-        float(softcap or 0.0), int(keep_first or 0), _stream()), "rl_attention_decode")
+        float(softcap or 0.0), int(keep_first or 0), int(bool(gate_per_head and gate is not None)), _stream()), "rl_attention_decode")
     _count(2 if num_splits > 1 and not cluster else 1)
 
 
@@ -1443,7 +1451,8 @@ def attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
                          cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, kv_lens: torch.Tensor, q_lens,
                          out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                          window: int = 0, tile_order: Optional[torch.Tensor] = None, sink: bool = False,
-                         gate: Optional[torch.Tensor] = None, softcap: float = 0.0, keep_first: int = 0, chunk: int = 0) -> None:
+                         gate: Optional[torch.Tensor] = None, softcap: float = 0.0, keep_first: int = 0, chunk: int = 0,
+                         gate_per_head: bool = False) -> None:
     """The same as ``attention_prefill`` on tcgen05 tensor cores (head size 64 or 128).  ``chunk`` > 0 (instead of a
     window): a query at position p sees positions [p - p % chunk, p].  The cache
     pools must hold finite values everywhere (the cache zero-fills them when it allocates them).
@@ -1460,13 +1469,13 @@ def attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
         _need(tile_order, "tile_order", torch.int32)
         assert tile_order.numel() == 2 * tiles
     ldq = q.stride(0) if q.shape[0] > 1 else max(q.stride(0), num_heads * head_dim)
-    gptr, ldg = _gate_args(gate, q.shape[0], num_heads * head_dim, 16)
-    _check(library().rl_attention_prefill_tc_shaped(
+    gptr, ldg = _gate_args(gate, q.shape[0], num_heads, 2) if gate_per_head else _gate_args(gate, q.shape[0], num_heads * head_dim, 16)
+    _check(library().rl_attention_prefill_tc_headgate(
         q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0], page_table.data_ptr(),
         page_table.shape[1], cu_seqlens.data_ptr(), seq_slots.data_ptr(), kv_lens.data_ptr(), B, tiles, q.shape[0],
         out.data_ptr(), out.stride(0), num_heads, num_kv_heads, head_dim, float(scale), int(window),
         _tc_error_word(q.device).data_ptr(), _ptr(tile_order), int(bool(sink)), gptr, ldg, float(softcap or 0.0),
-        int(keep_first or 0), int(chunk or 0), _stream()), "rl_attention_prefill_tc")
+        int(keep_first or 0), int(chunk or 0), int(bool(gate_per_head and gate is not None)), _stream()), "rl_attention_prefill_tc")
     _count()
 
 
@@ -1538,7 +1547,12 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
         attention_shared_key(q, k_pool, page_table, step.cu_seqlens, step.seq_slots, step.kv_lens, step.q_lens, out,
                              num_heads, head_dim, head_dim if value_dim is None else value_dim, scale, window, gate=gate)
         return
-    if values_in_keys or gate_per_head:
+    vd_eff = head_dim if value_dim is None else value_dim
+    tc_head_gate = (gate_per_head and gate is not None and not values_in_keys and vd_eff == head_dim and q.dtype == torch.bfloat16
+                    and not chunk and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+                    and (attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim) if step.is_decode else
+                         attention_prefill_tc_supported(q.dtype, num_heads, num_kv_heads, head_dim)))
+    if values_in_keys or (gate_per_head and not tc_head_gate):
         attention_simt(q, k_pool, v_pool, page_table, step.slot_of_token, step.positions, out,
                        num_heads, num_kv_heads, head_dim, scale, window, value_dim=value_dim, sink=sink, gate=gate,
                        softcap=softcap, keep_first=keep_first, chunk=chunk, values_in_keys=values_in_keys,
@@ -1549,7 +1563,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
     masked = bool(softcap or (keep_first and window) or chunk)
     tc_prefill = (not step.is_decode and attention_prefill_tc_supported(q.dtype, num_heads, num_kv_heads, head_dim)
                   and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
-                  and (gate is None or (gate.data_ptr() % 16 == 0 and gate.stride(0) % 8 == 0)))
+                  and (gate is None or gate_per_head or (gate.data_ptr() % 16 == 0 and gate.stride(0) % 8 == 0)))
     if (value_dim is not None and value_dim != head_dim) or (masked and not tc_prefill and not (
             step.is_decode and attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim))):
         # soft-capped scores, kept first tokens and chunked masks: the any-shape kernel, the decode kernel and the
@@ -1573,7 +1587,8 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
                     order = derived[("decode_order", dec_window)] = decode_order(step.seq_slots, step.kv_lens, dec_window)
             attention_decode(q, k_pool, v_pool, page_table, step.seq_slots, step.kv_lens, out,
                              num_heads, num_kv_heads, head_dim, scale, dec_window, num_splits=cluster, plan=order,
-                             cluster=cluster > 1, sink=sink, gate=gate, softcap=softcap, keep_first=keep_first)
+                             cluster=cluster > 1, sink=sink, gate=gate, softcap=softcap, keep_first=keep_first,
+                             gate_per_head=gate_per_head)
             return
         plan = None
         derived = getattr(step, "derived", None)     # what layers of one step share
@@ -1584,7 +1599,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
                 plan = derived[key] = decode_plan(step.seq_slots, step.kv_lens, dec_window, splits)
         attention_decode(q, k_pool, v_pool, page_table, step.seq_slots, step.kv_lens, out,
                          num_heads, num_kv_heads, head_dim, scale, dec_window, num_splits=splits, plan=plan, sink=sink, gate=gate,
-                         softcap=softcap, keep_first=keep_first)
+                         softcap=softcap, keep_first=keep_first, gate_per_head=gate_per_head)
         return
     if tc_prefill:
         order = None
@@ -1595,7 +1610,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
                 order = derived["prefill_tile_order"] = prefill_tile_order(step.q_lens, step.kv_lens_host, q.device)
         attention_prefill_tc(q, k_pool, v_pool, page_table, step.cu_seqlens, step.seq_slots, step.kv_lens,
                              step.q_lens, out, num_heads, num_kv_heads, head_dim, scale, window, tile_order=order,
-                             sink=sink, gate=gate, softcap=softcap, keep_first=keep_first, chunk=chunk)
+                             sink=sink, gate=gate, softcap=softcap, keep_first=keep_first, chunk=chunk, gate_per_head=gate_per_head)
         return
     if not chunk and not step.is_decode and attention_prefill_supported(q.dtype, num_heads, num_kv_heads, head_dim) \
             and (gate is None or (gate.data_ptr() % 4 == 0 and gate.stride(0) % 2 == 0)):

@@ -168,7 +168,10 @@ class GQAttention(Mixer):
         M = xn.shape[0]
         dt = xn.dtype
         n_qkv = (H + G) * hd + (0 if self.value_from_key else G * vd)
-        qkv = torch.empty((M, n_qkv + self.gate_rows), dtype=dt, device=xn.device)
+        width = n_qkv + self.gate_rows
+        # rows a multiple of 8 elements apart (the tensor-core attention kernels read queries by 16-byte pieces): a gate of
+        # one number a head can leave the row's length odd
+        qkv = torch.empty((M, -(-width // 8) * 8 if self.gate_per_head else width), dtype=dt, device=xn.device)[:, :width]
         v_other = v_mix = None
         if self.value_mix is not None and self.value_mix["role"] == "blend":
             v_other = getattr(step, "derived", {}).get(("values", self.value_mix["key"]))

@@ -140,7 +140,7 @@ class MoEMLP(FeedForward):
                 K.moe_experts(xn, wgu, wd, ids, weights, residual, interleaved=True)
         else:
             K.moe_experts(xn, self.wgu.view(self.E, 2, self.F, self.d), wd, ids, weights, residual)
-        if self.shared_gated:
+        if self.shared_gated and self.shared is not None:
             (y, _), = self.shared.forward_out(xn, step)
             K.row_gate_add(residual, y, xn, self.shared_gate)
         elif self.shared is not None:

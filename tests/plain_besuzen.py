@@ -180,7 +180,10 @@ def route(scores: torch.Tensor, top: int, groups: int, keep: int):
     return cand, chosen / (chosen.sum() + 1e-20)
 
 
-def experts_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mlp: dict) -> torch.Tensor:
+def experts_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mlp: dict, forced: Optional[Dict[int, List[int]]] = None) -> torch.Tensor:
+    """``forced`` {position: expert ids}: the experts of these tokens are given instead of chosen (their weights are
+    still the plain scores, renormalised): a comparison with a run in fewer bits takes that run's choices where a
+    close call may have fallen the other way, so that it measures rounding and not the choice."""
     r = mlp["router"]
     g = r.get("groups") or {}
     out = torch.zeros_like(h)
@@ -190,6 +193,9 @@ def experts_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mlp: dict) -
         s = torch.exp(z - z.max())
         s = s / s.sum()
         ids, weights = route(s, r["top"], g.get("count", 1), g.get("keep", 1))
+        if forced is not None and t in forced:
+            ids = list(forced[t])
+            weights = s[ids] / (s[ids].sum() + 1e-20)
         for e, wt in zip(ids, weights):
             out[t] += wt * gated_ff(h[t:t + 1], w, f"{p}e{e}.", silu)[0]
     if mlp.get("shared") is not None:
@@ -198,10 +204,12 @@ def experts_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mlp: dict) -
 
 
 # --------------------------------------------------------------------------- the model
-def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], layers_out: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
-    """Logits [T, V] of one whole sequence; ``layers_out`` collects the stream after every layer."""
+def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], layers_out: Optional[List[torch.Tensor]] = None,
+            forced: Optional[Dict[int, Dict[int, List[int]]]] = None) -> torch.Tensor:
+    """Logits [T, V] of one whole sequence; ``layers_out`` collects the stream after every layer; ``forced``
+    {layer: {position: expert ids}}: see ``experts_ff``."""
     eps = cfg["norm"]["eps"]
-    x = w["embed"][list(tokens)] * cfg["embedding"]["scale"]
+    x = w["embed"][list(tokens)] * (cfg.get("embedding") or {}).get("scale", 1.0)
     v_first = None
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
@@ -224,8 +232,8 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], layers
             if mlp["kind"] == "dense":
                 y = y + gated_ff(h2, w, p + "mlp.", gelu_tanh)
             else:
-                y = y + experts_ff(h2, w, p + "mlp.", mlp)
+                y = y + experts_ff(h2, w, p + "mlp.", mlp, None if forced is None else forced.get(i))
         x = x + y
         if layers_out is not None:
             layers_out.append(x.clone())
-    return (layer_norm(x, w["final.norm"], eps) @ w["head"].T) * cfg["logit_scale"]
+    return (layer_norm(x, w["final.norm"], eps) @ w["head"].T) * cfg.get("logit_scale", 1.0)
