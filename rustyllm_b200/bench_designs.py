@@ -102,7 +102,7 @@ def forilorn_config(s: dict, window: int = 1024) -> dict:
 def besuzen_config(s: dict) -> dict:
     d, H, G, hd = s["width"], s["heads"], s["kv_heads"], s["dim"]
     att = {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5}
-    rotated = dict(att, rot={"base": 500000.0, "dims": hd}, v_mix=True)
+    rotated = dict(att, rot={"base": 1.0e6, "dims": hd}, v_mix=True)
     right = {"heads": d // 64, "dim": 64, "decay_rank": 64}
     dense = {"kind": "dense", "ff": s["ff"]}
     moe = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"], "groups": {"count": 4, "keep": 2}},
@@ -112,11 +112,11 @@ def besuzen_config(s: dict) -> dict:
         mlp = moe if i % 2 else dense
         if i % 2 == 0:
             layers.append({"type": "parallel", "mlp": mlp,
-                           "mixer": {"left": dict(att), "right": dict(right), "left_scale": 0.6, "right_scale": 0.5}})
+                           "mixer": {"left": dict(att), "right": dict(right), "left_scale": 0.7, "right_scale": 0.4}})
         else:
             layers.append({"type": "attention", "mixer": dict(rotated), "mlp": mlp})
-    return {"architecture": "Besuzen", "vocab": s["vocab"], "width": d, "norm": {"eps": 1e-6}, "embedding": {"scale": 3.0},
-            "logit_scale": 2.0, "layers": layers}
+    return {"architecture": "Besuzen", "vocab": s["vocab"], "width": d, "norm": {"eps": 1e-6}, "embedding": {"scale": 4.0},
+            "logit_scale": 0.5, "layers": layers}
 
 
 def measure(config: dict, prompt: int, batches: List[int], context: int, steps: int, warmup: int) -> Dict[str, float]:

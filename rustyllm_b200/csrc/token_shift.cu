@@ -19,7 +19,9 @@
 #define TS_THREADS 256
 #define TS_MAX_MIX 8
 
-template <typename T>
+// V consecutive elements a thread (V * sizeof(T) = 16 bytes where the rows allow it, else 1); blockIdx.y walks the row
+// in pieces of TS_THREADS * V elements, so that a step of few tokens still fills the machine.
+template <typename T, int V>
 __global__ void __launch_bounds__(TS_THREADS)
 token_shift_mix_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ mu, int n_mix, const int* __restrict__ positions,
                        const int* __restrict__ slot_of_token, const int* __restrict__ cu_seqlens, int num_seqs,
@@ -46,21 +48,35 @@ token_shift_mix_kernel(const T* __restrict__ h, int ldh, const float* __restrict
   __syncthreads();
   const bool first = s_first != 0;
   const bool fresh = positions[m] == 0;
-  const T* cur = h + (size_t)m * ldh;
-  const T* before = h + (size_t)(m - 1) * ldh;          // read only where the row in front is the same sequence's
-  const T* tail = h + (size_t)s_last * ldh;
-  float* st = state + (size_t)slot * state_stride;
-  for (int i = threadIdx.x; i < d; i += TS_THREADS) {
-    const float c = rl_ld(cur + i);
-    float p;
-    if (!first) p = rl_ld(before + i);
-    else {
-      p = fresh ? 0.f : st[i];
-      st[i] = rl_ld(tail + i);                           // this thread alone reads and writes element i of the state
-    }
-    const float diff = p - c;
-    for (int s = 0; s < n_mix; ++s)
-      rl_st(out + ((size_t)s * M + m) * d + i, fmaf(diff, mu[(size_t)s * d + i], c));
+  const int i = (blockIdx.y * TS_THREADS + threadIdx.x) * V;
+  if (i >= d) return;
+  const T* cur = h + (size_t)m * ldh + i;
+  float* st = state + (size_t)slot * state_stride + i;
+  struct alignas(V * sizeof(T)) Pack { T e[V]; };
+  float c[V], p[V];
+  {
+    const Pack pk = *reinterpret_cast<const Pack*>(cur);
+#pragma unroll
+    for (int k = 0; k < V; ++k) c[k] = rl_ld(&pk.e[k]);
+  }
+  if (!first) {                        // the row in front belongs to the same sequence
+    const Pack pk = *reinterpret_cast<const Pack*>(cur - ldh);
+#pragma unroll
+    for (int k = 0; k < V; ++k) p[k] = rl_ld(&pk.e[k]);
+  } else {
+    // this thread alone reads and writes its elements of the state: the old value first, then the sequence's last
+    // input of the step
+#pragma unroll
+    for (int k = 0; k < V; ++k) p[k] = fresh ? 0.f : st[k];
+    const Pack pk = *reinterpret_cast<const Pack*>(h + (size_t)s_last * ldh + i);
+#pragma unroll
+    for (int k = 0; k < V; ++k) st[k] = rl_ld(&pk.e[k]);
+  }
+  for (int s = 0; s < n_mix; ++s) {
+    Pack o;
+#pragma unroll
+    for (int k = 0; k < V; ++k) rl_st(&o.e[k], fmaf(p[k] - c[k], mu[(size_t)s * d + i + k], c[k]));
+    *reinterpret_cast<Pack*>(out + ((size_t)s * M + m) * d + i) = o;
   }
 }
 
@@ -134,14 +150,20 @@ extern "C" int rl_token_shift_mix(const void* h, int ldh, int dtype, const float
   RL_REQUIRE(state != nullptr && state_stride >= width, "rl_token_shift_mix: no state, or its rows are shorter than %d", width);
   if (num_tokens == 0) return RL_OK;
   RL_REQUIRE(num_seqs > 0, "rl_token_shift_mix: tokens without a sequence");
-  if (dtype == RL_F32)
-    rl_launch_pdl(token_shift_mix_kernel<float>, num_tokens, TS_THREADS, 0, stream, (const float*)h, ldh, mu, n_mix, positions, slot_of_token,
-                  cu_seqlens, num_seqs, state, state_stride, (float*)out, num_tokens, width);
-  else if (dtype == RL_BF16)
-    rl_launch_pdl(token_shift_mix_kernel<__nv_bfloat16>, num_tokens, TS_THREADS, 0, stream, (const __nv_bfloat16*)h, ldh, mu, n_mix, positions,
-                  slot_of_token, cu_seqlens, num_seqs, state, state_stride, (__nv_bfloat16*)out, num_tokens, width);
-  else
+  const int esz = dtype == RL_F32 ? 4 : 2, vec = 16 / esz;
+  const bool wide = width % vec == 0 && ldh % vec == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)out & 15) == 0;
+  const dim3 grid(num_tokens, (width + TS_THREADS * (wide ? vec : 1) - 1) / (TS_THREADS * (wide ? vec : 1)));
+#define TS_GO(T, V)                                                                                                                   \
+  rl_launch_pdl(token_shift_mix_kernel<T, V>, grid, TS_THREADS, 0, stream, (const T*)h, ldh, mu, n_mix, positions, slot_of_token, cu_seqlens, \
+                num_seqs, state, state_stride, (T*)out, num_tokens, width)
+  if (dtype == RL_F32) {
+    if (wide) TS_GO(float, 4); else TS_GO(float, 1);
+  } else if (dtype == RL_BF16) {
+    if (wide) TS_GO(__nv_bfloat16, 8); else TS_GO(__nv_bfloat16, 1);
+  } else {
     RL_REQUIRE(false, "rl_token_shift_mix: unknown dtype %d", dtype);
+  }
+#undef TS_GO
   RL_LAUNCH_CHECK("rl_token_shift_mix");
   return RL_OK;
 }

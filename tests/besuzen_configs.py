@@ -80,11 +80,11 @@ CONFIGS = {
     # heads of 64 with values as wide as keys (the tensor-core attention kernels take the element-wise gate), three
     # blending layers around a parallel layer with a time mixer of 64-wide heads, experts in four groups of which one
     # is kept, one expert a token
-    "C": {"architecture": "Besuzen", "vocab": 211, "width": 128, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.5}, "logit_scale": 2.0,
-          "layers": [attention(att(4, 2, 64, 64, 0.125, rot=(64, 500000.0), v_mix=True), dense(96)),
+    "C": {"architecture": "Besuzen", "vocab": 211, "width": 128, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.5}, "logit_scale": 1.8,
+          "layers": [attention(att(4, 2, 64, 64, 0.125, rot=(64, 300000.0), v_mix=True), dense(96)),
                      attention(att(2, 2, 64, 64, 0.125, rot=(32, 10000.0), v_mix=True), moe(8, 1, 32, groups=(4, 1), shared=32)),
-                     parallel(att(2, 2, 64, 64, 0.11), 2, 64, 0.6, 0.5, moe(4, 2, 24, groups=(2, 2))),
-                     attention(att(4, 2, 64, 64, 0.125, rot=(64, 500000.0), v_mix=True), dense(64))]},
+                     parallel(att(2, 2, 64, 64, 0.11), 2, 64, 0.75, 0.45, moe(4, 2, 24, groups=(2, 2))),
+                     attention(att(4, 2, 64, 64, 0.125, rot=(64, 300000.0), v_mix=True), dense(64))]},
 }
 
 
@@ -195,7 +195,7 @@ def random_config(seed: int):
         if v_mix_shape is not None:
             G, dv = v_mix_shape
             H = G * pick(1, 2)
-        rot = (pick(4, 8, dk), pick(100.0, 10000.0, 500000.0)) if rot_ok else None
+        rot = (pick(4, 8, dk), pick(100.0, 10000.0, 300000.0)) if rot_ok else None
         return att(H, G, dk, dv, 1.0 / math.sqrt(dk), rot=rot, v_mix=v_mix_shape is not None)
 
     def rand_mlp():
@@ -213,7 +213,7 @@ def random_config(seed: int):
     layers = []
     for _ in range(pick(2, 3, 4)):
         if pick(0, 1):
-            layers.append(parallel(rand_att(rot_ok=False), pick(1, 2, 3), pick(8, 16, 24), pick(1.0, 0.6), pick(1.0, 0.5, 1.5), rand_mlp()))
+            layers.append(parallel(rand_att(rot_ok=False), pick(1, 2, 3), pick(8, 16, 24), pick(1.0, 0.65), pick(1.0, 0.45, 1.5), rand_mlp()))
         else:
             layers.append(attention(rand_att(v_mix_shape=mix_shape if pick(0, 1, 1) else None), rand_mlp()))
     cfg = {"architecture": "Besuzen", "vocab": pick(31, 64, 150), "width": d, "norm": {"eps": pick(1e-5, 1e-6)},
