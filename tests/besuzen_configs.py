@@ -185,7 +185,7 @@ def random_config(seed: int):
 
     def pick(*xs):
         return xs[int(torch.randint(0, len(xs), (1,), generator=r))]
-    d = pick(24, 36, 40, 64, 72)
+    d = pick(24, 36, 40, 50, 64, 72)
 
     def rand_att(v_mix_shape=None, rot_ok=True):
         G = pick(1, 2, 3)

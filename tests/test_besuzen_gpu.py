@@ -401,7 +401,8 @@ def test_gated_product_with_the_gelu_on_the_gate(M):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,G,hd,vd,per_head", [(4, 1, 16, 8, True), (6, 3, 24, 16, False), (2, 2, 64, 64, False), (4, 2, 64, 64, True)])
+@pytest.mark.parametrize("H,G,hd,vd,per_head", [(4, 1, 16, 8, True), (6, 3, 24, 16, False), (2, 2, 64, 64, False), (4, 2, 64, 64, True),
+                                                 (3, 1, 128, 128, True), (2, 2, 128, 128, False)])
 def test_one_far_key_stands_out_in_prompts_and_in_decoding(dtype, H, G, hd, vd, per_head):
     """A key hundreds of positions back, at a page's last place, outscores all others by 12: the output must be its
     value (times the gate), in a prompt portion that starts behind it and in single tokens; the key in front of
