@@ -47,7 +47,7 @@ linear_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, in
   // tile is walked, so that no load from global memory is waited for.  Few tokens (NPT > 8, 8 lanes a column): a
   // lane holds rows r, r + 8, ... (the state's loads and stores are whole lines), staged directly.
   constexpr bool LONG = NPT <= 8;
-  static_assert(!LONG || (R * SCAN_COLS >= SCAN_TILE * SCAN_COLS && NPT % 4 == 0), "the long shape stages a tile's values one a thread");
+  static_assert(!LONG || (R * SCAN_COLS >= SCAN_TILE * SCAN_COLS && (NPT % 4 == 0 || NPT == 2)), "the long shape stages a tile's values one a thread");
   // rows beyond dk are staged as zeros, so the walk needs no bounds: their state stays zero
   __shared__ __align__(16) float s_q[SCAN_TILE][DKP], s_k[SCAN_TILE][DKP];
   __shared__ float s_v[SCAN_TILE][SCAN_COLS], s_bv[SCAN_TILE][SCAN_COLS], s_a[SCAN_TILE];
@@ -154,7 +154,23 @@ linear_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, in
       part[tt] = 0.f;
       if (tt < nt) {
         const float a = s_a[tt], bv = s_bv[tt][c];
-        if (LONG) {
+        if constexpr (LONG && NPT == 2) {
+          // two rows a lane (32 lanes a column of 64 rows): twice the warps of the four-row shape for one more shuffle
+          const float2 kk = *reinterpret_cast<const float2*>(&s_k[tt][2 * r]), qq = *reinterpret_cast<const float2*>(&s_q[tt][2 * r]);
+          if constexpr (CH) {
+            const float2 ww = *reinterpret_cast<const float2*>(&s_w[tt][2 * r]);
+            const float p0 = bv * kk.x, p1 = bv * kk.y;
+            part[tt] = fmaf(fmaf(U[0], p0, S[0]), qq.x, part[tt]);
+            part[tt] = fmaf(fmaf(U[1], p1, S[1]), qq.y, part[tt]);
+            S[0] = fmaf(ww.x, S[0], p0);
+            S[1] = fmaf(ww.y, S[1], p1);
+          } else {
+            S[0] = fmaf(a, S[0], bv * kk.x);
+            S[1] = fmaf(a, S[1], bv * kk.y);
+            part[tt] = fmaf(S[0], qq.x, part[tt]);
+            part[tt] = fmaf(S[1], qq.y, part[tt]);
+          }
+        } else if (LONG) {
           const float4* k4 = reinterpret_cast<const float4*>(&s_k[tt][NPT * r]);
           const float4* q4 = reinterpret_cast<const float4*>(&s_q[tt][NPT * r]);
 #pragma unroll
@@ -233,7 +249,10 @@ static int scan_launch(const void* q, int ldq, const void* k, int ldk, const voi
   if (!wide) {                      // few tokens a sequence: the state's traffic is the work; 8 lanes a column
     if (dk <= 128) SCAN_GO(16, 8, 16);
     else SCAN_GO(32, 8, 16);
-  } else if (dk <= 64) SCAN_GO(4, 16, 8);
+  } else if (dk <= 64) {
+    if constexpr (CH) SCAN_GO(2, 32, 16);
+    else SCAN_GO(4, 16, 8);
+  }
   else if (dk <= 128) SCAN_GO(4, 32, 8);
   else SCAN_GO(8, 32, 8);
 #undef SCAN_GO
