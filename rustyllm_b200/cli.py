@@ -304,7 +304,7 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool, layer_index: int = 0)
     if hasattr(att, "wqkv"):
         qkv = product_rows("attn_qkv", att.wqkv, att.bqkv, att.wo, att.bo)
     for m, tag in ((other, "mixer2_in"), (None if hasattr(att, "wqkv") else att, "mixer_in")):
-        w_in = next((getattr(m, n) for n in ("w_in", "wqkvg", "wr") if m is not None and getattr(m, n, None) is not None), None)
+        w_in = next((getattr(m, n) for n in ("w_in", "wqkvg", "wrkvg") if m is not None and getattr(m, n, None) is not None), None)
         if w_in is not None:
             product_rows(tag, w_in, None, m.wo, None)
     from .parts.mlp import GatedMLP

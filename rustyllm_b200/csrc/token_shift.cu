@@ -1,7 +1,7 @@
 // Small kernels around a mixer that reads, beside a token's input h_t, the previous token's h_{t-1}:
 //
 // rl_token_shift_mix  n blends of the two, m_s = h_t + (h_{t-1} - h_t) * mu_s  (s = 0 .. n-1, mu_s a vector), in
-//                     32-bit, stored in the compute dtype as [n, M, d].  The previous token's input is the row in
+//                     32-bit, stored in the compute dtype as [n, rows >= M, d].  The previous token's input is the row in
 //                     front where that row belongs to the same sequence, the sequence's state (float [d] a slot,
 //                     the last input it was fed) where the step's first token of a sequence continues one under
 //                     way, and zero at position 0.  The block of a sequence's first token of the step, the only
@@ -25,7 +25,7 @@ template <typename T, int V>
 __global__ void __launch_bounds__(TS_THREADS)
 token_shift_mix_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ mu, int n_mix, const int* __restrict__ positions,
                        const int* __restrict__ slot_of_token, const int* __restrict__ cu_seqlens, int num_seqs,
-                       float* __restrict__ state, long long state_stride, T* __restrict__ out, int M, int d) {
+                       float* __restrict__ state, long long state_stride, T* __restrict__ out, int M, int d, long long blend_rows) {
   __shared__ int s_first, s_last;
   rl_pdl_trigger();
   rl_pdl_wait();
@@ -76,7 +76,7 @@ token_shift_mix_kernel(const T* __restrict__ h, int ldh, const float* __restrict
     Pack o;
 #pragma unroll
     for (int k = 0; k < V; ++k) rl_st(&o.e[k], fmaf(p[k] - c[k], mu[(size_t)s * d + i + k], c[k]));
-    *reinterpret_cast<Pack*>(out + ((size_t)s * M + m) * d + i) = o;
+    *reinterpret_cast<Pack*>(out + ((size_t)s * blend_rows + m) * d + i) = o;
   }
 }
 
@@ -141,11 +141,12 @@ scale_kernel(float* __restrict__ y, size_t n, float s) {
   if (i < n) y[i] *= s;
 }
 
-// h [M, ldh] and out [n_mix, M, d] in `dtype`; mu float [n_mix, d]; state float, [d] of slot s at state + s * state_stride.
+// h [M, ldh] and out [n_mix, blend_rows, d] in `dtype` (blend_rows >= M: every blend's rows may be padded, e.g. to whole
+// tiles of a product that reads them; rows beyond M are not written); mu float [n_mix, d]; state float, [d] of slot s at state + s * state_stride.
 extern "C" int rl_token_shift_mix(const void* h, int ldh, int dtype, const float* mu, int n_mix, const int* positions,
                                   const int* slot_of_token, const int* cu_seqlens, int num_seqs, float* state, long long state_stride,
-                                  void* out, int num_tokens, int width, cudaStream_t stream) {
-  RL_REQUIRE(num_tokens >= 0 && width > 0 && ldh >= width && num_seqs >= 0, "rl_token_shift_mix: bad sizes");
+                                  void* out, int blend_rows, int num_tokens, int width, cudaStream_t stream) {
+  RL_REQUIRE(num_tokens >= 0 && width > 0 && ldh >= width && num_seqs >= 0 && blend_rows >= num_tokens, "rl_token_shift_mix: bad sizes");
   RL_REQUIRE(n_mix > 0 && n_mix <= TS_MAX_MIX, "rl_token_shift_mix: %d blends outside [1, %d]", n_mix, TS_MAX_MIX);
   RL_REQUIRE(state != nullptr && state_stride >= width, "rl_token_shift_mix: no state, or its rows are shorter than %d", width);
   if (num_tokens == 0) return RL_OK;
@@ -155,7 +156,7 @@ extern "C" int rl_token_shift_mix(const void* h, int ldh, int dtype, const float
   const dim3 grid(num_tokens, (width + TS_THREADS * (wide ? vec : 1) - 1) / (TS_THREADS * (wide ? vec : 1)));
 #define TS_GO(T, V)                                                                                                                   \
   rl_launch_pdl(token_shift_mix_kernel<T, V>, grid, TS_THREADS, 0, stream, (const T*)h, ldh, mu, n_mix, positions, slot_of_token, cu_seqlens, \
-                num_seqs, state, state_stride, (T*)out, num_tokens, width)
+                num_seqs, state, state_stride, (T*)out, num_tokens, width, (long long)blend_rows)
   if (dtype == RL_F32) {
     if (wide) TS_GO(float, 4); else TS_GO(float, 1);
   } else if (dtype == RL_BF16) {

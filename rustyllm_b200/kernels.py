@@ -43,7 +43,7 @@ _SIGNATURES = {
                      _c_int, _c_int, _c_void_p],
     "rl_layer_norm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_float, _c_void_p],
     "rl_token_shift_mix": [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll,
-                           _c_void_p, _c_int, _c_int, _c_void_p],
+                           _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "rl_tanh_cast": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
     "rl_scaled_add": [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_float, _c_ll, _c_void_p],
     "rl_row_gate_add": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
@@ -440,6 +440,37 @@ def moe_experts_grouped(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tens
     _count(5)
 
 
+_TILE_GROUPS = {}
+
+
+def gemm_tc_row_groups_tile(rows: int) -> int:
+    """The token tile for ``gemm_tc_row_groups`` at ``rows`` rows a group (each group is padded to whole tiles)."""
+    return 16 if rows <= 16 else 32 if rows <= 32 else 64 if rows <= 64 else 128 if rows <= 1024 else 256
+
+
+def gemm_tc_row_groups_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.is_contiguous() and w.is_contiguous() and a.shape[-1] % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc_row_groups(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile: int) -> None:
+    """Several products of equal shape with inputs and weights of their own as one grouped tensor-core product:
+    out[g] = a[g] @ w[g].T for a [G, rows, K], w [G, N, K], out [G, rows, N], all bfloat16 and contiguous, ``rows`` a
+    multiple of ``tile`` (the caller pads; what the padding rows hold does not matter, every row is computed by itself)."""
+    _need(a, "a", torch.bfloat16); _need(w, "w", torch.bfloat16); _need(out, "out", torch.bfloat16)
+    G, rows, Kd = a.shape
+    N = w.shape[1]
+    assert w.shape == (G, N, Kd) and out.shape == (G, rows, N) and rows % tile == 0
+    per = rows // tile
+    key = (a.device, G, per)
+    table = _TILE_GROUPS.get(key)
+    if table is None:
+        table = _TILE_GROUPS[key] = torch.arange(G * per, dtype=torch.int32, device=a.device).div(per, rounding_mode="floor").to(torch.int32)
+    _check(library().rl_gemm_tc_grouped(a.data_ptr(), w.data_ptr(), out.data_ptr(), OUT_SAME, G * rows, N, Kd, Kd, N,
+                                        _tc_error_word(a.device).data_ptr(), table.data_ptr(), G, tile, _stream()), "rl_gemm_tc_grouped")
+    _count()
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
             rows: Optional[torch.Tensor] = None) -> None:
     """out[r] = rms_norm(x[rows[r]] if rows is given else x[r]) * weight."""
@@ -618,17 +649,18 @@ def token_shift_mix(h: torch.Tensor, mu: torch.Tensor, positions: torch.Tensor, 
                     state: torch.Tensor, out: torch.Tensor) -> None:
     """out[s, m] = h[m] + (previous(m) - h[m]) * mu[s] for the n rows of ``mu`` (float32 [n, d]); previous(m) is the
     row in front where it belongs to the same sequence, else the sequence's state (float [d] a slot; zero at position
-    0).  Leaves every sequence's last row of the step in its state.  h [M, d] (a view is fine), out [n, M, d]."""
+    0).  Leaves every sequence's last row of the step in its state.  h [M, d] (a view is fine), out [n, rows >= M, d]
+    (rows beyond M, padding for a product that reads whole tiles, are left as they are)."""
     _need(h, "h", contiguous=False); _need(mu, "mu", torch.float32); _need(out, "out", h.dtype)
     _need(positions, "positions", torch.int32); _need(slot_of_token, "slot_of_token", torch.int32); _need(cu_seqlens, "cu_seqlens", torch.int32)
     M, d = h.shape
     n = mu.shape[0]
-    assert mu.shape == (n, d) and out.shape == (n, M, d) and h.stride(1) == 1
+    assert mu.shape == (n, d) and out.shape[0] == n and out.shape[1] >= M and out.shape[2] == d and h.stride(1) == 1
     sp, ss = _state_args(state)
     assert state.shape[1] >= 4 * d
     _check(library().rl_token_shift_mix(h.data_ptr(), h.stride(0) if M > 1 else d, _dt(h), mu.data_ptr(), n, positions.data_ptr(),
                                         slot_of_token.data_ptr(), cu_seqlens.data_ptr(), cu_seqlens.numel() - 1, sp, ss, out.data_ptr(),
-                                        M, d, _stream()), "rl_token_shift_mix")
+                                        out.shape[1], M, d, _stream()), "rl_token_shift_mix")
     _count()
 
 

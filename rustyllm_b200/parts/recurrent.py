@@ -187,14 +187,14 @@ class ShiftedDecayRecurrence(_StateMixer):
         self.eps = float(norm_eps)
         self.names = names
         self._shift_bytes = _aligned(4 * hidden_size)
-        self.mu = self.wr = self.wk = self.wv = self.wg = self.w1 = self.w2 = self.w0 = self.u = self.norm_w = self.wo = None
+        self.mu = self.wrkvg = self.w1 = self.w2 = self.w0 = self.u = self.norm_w = self.wo = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         d, inner, n = self.d, self.H * self.n, self.names
         sfx = n.get("suffix", ".weight")
         specs = {"mu": ParamSpec(tuple(ParamSource(n["mu"] + s, (d,)) for s in self.MIXES), role="vector", init="normal")}
-        for key in ("r", "k", "v", "g"):
-            specs["w" + key] = ParamSpec((ParamSource(n[key] + sfx, (inner, d)),))
+        # the four projections one behind the other, [4 * inner, d]: one grouped product reads each blend with its own rows
+        specs["wrkvg"] = ParamSpec(tuple(ParamSource(n[key] + sfx, (inner, d)) for key in ("r", "k", "v", "g")))
         specs.update({
             "w1": ParamSpec((ParamSource(n["w1"] + sfx, (self.rank, d)),)),
             "w2": ParamSpec((ParamSource(n["w2"] + sfx, (inner, self.rank)),)),
@@ -220,11 +220,21 @@ class ShiftedDecayRecurrence(_StateMixer):
         dt, dev = xn.dtype, xn.device
         state = self._state(cache)
         shift_state, scan_state = state[:, :self._shift_bytes], state[:, self._shift_bytes:]
-        mixes = torch.empty((len(self.MIXES), M, self.d), dtype=dt, device=dev)
+        w4 = self.wrkvg.view(4, inner, self.d)
+        grouped = K.gemm_tc_row_groups_supported(xn, w4) and inner % 8 == 0
+        tile = K.gemm_tc_row_groups_tile(M) if grouped else 1
+        # every blend's rows padded to whole tiles of the grouped product; what the padding holds is never looked at
+        # (every row of a product is computed by itself, and the padding's results are not read)
+        rows = -(-M // tile) * tile
+        mixes = torch.empty((len(self.MIXES), rows, self.d), dtype=dt, device=dev)
         K.token_shift_mix(xn, self.mu, step.positions, step.slot_of_token, step.cu_seqlens, shift_state, mixes)
-        proj = torch.empty((4, M, inner), dtype=dt, device=dev)          # r, k, v, g
-        for i, w in enumerate((self.wr, self.wk, self.wv, self.wg)):
-            linear(mixes[i], w, proj[i], OUT_SAME)
+        proj = torch.empty((4, rows, inner), dtype=dt, device=dev)          # r, k, v, g
+        if grouped:
+            K.gemm_tc_row_groups(mixes[:4], w4, proj, tile)
+        else:
+            for i in range(4):
+                linear(mixes[i], w4[i], proj[i], OUT_SAME)
+        mixes, proj = mixes[:, :M], proj[:, :M]
         # the decay: the first projection's output and its tanh in 32-bit, the second projection's output (the decay's
         # logarithm's logarithm, with its offset) in 32-bit; the scan forms exp(-exp(.)) itself
         low = torch.empty((M, self.rank), dtype=torch.float32, device=dev)
